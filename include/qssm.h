@@ -1,0 +1,171 @@
+/*
+ * qssm.h - C ABI of the B200 (sm_100a) gated linear scan
+ *
+ *     h(t) = a(t) * h(t-1) + b(t) * x(t),   y(t) = c(t) * h(t),   h(-1) = h_in (default 0)
+ *
+ * over [B, L, D] tensors whose innermost (D) axis is contiguous; one
+ * independent recurrence per (b, d).  Storage types are fp32, fp16 or bf16;
+ * all arithmetic is fp32.
+ *
+ * Conventions shared by every entry point
+ *   - every pointer is a DEVICE pointer unless the parameter says "host";
+ *   - strides are in ELEMENTS (stride_b between batches, stride_l between time
+ *     steps); the D stride is 1;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *   - the library allocates no device memory, never synchronises and keeps no
+ *     state between calls; scratch comes from the caller (`ws`, sized by
+ *     qssm_workspace_bytes);
+ *   - return value: 0 ok; < 0 bad argument (QSSM_E_*); > 0 a cudaError_t from
+ *     a launch.  Errors found on the device while a kernel runs (a bounded
+ *     wait that expired) are reported through `status_word`, an int the
+ *     caller owns (device memory or pinned host memory reachable from the
+ *     device; may be NULL): 0 = ok, otherwise a QSSM_S_* code.
+ *
+ * Each entry point names the interface of the reference implementation
+ * (samblouir/quick_ssm, paths inside that project) it replaces.
+ */
+#ifndef QSSM_H
+#define QSSM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* storage dtypes */
+#define QSSM_F32 0
+#define QSSM_F16 1
+#define QSSM_BF16 2
+
+/* argument errors (negative return values) */
+#define QSSM_E_NULL (-1)      /* a required pointer is NULL */
+#define QSSM_E_SHAPE (-2)     /* negative size, or a size beyond what the kernels index */
+#define QSSM_E_DTYPE (-3)     /* unknown dtype or unsupported in/out dtype pair */
+#define QSSM_E_STRIDE (-4)    /* stride smaller than the extent it must step over */
+#define QSSM_E_NEED_H (-5)    /* backward needs tile_h or h_saved */
+#define QSSM_E_WS (-6)        /* workspace too small for the requested segment count */
+#define QSSM_E_DRIVER (-7)    /* the CUDA driver entry point for tensor maps is unavailable */
+
+/* device-side status codes written to *status_word */
+#define QSSM_S_OK 0
+#define QSSM_S_TMA_TIMEOUT 1  /* a bounded wait on a bulk-copy barrier expired */
+
+/* Rows of time covered by one entry of the `tile_h` boundary-state array. */
+#define QSSM_TILE_ROWS 16
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int qssm_version(void);
+
+/* Text for a return value of any entry point or for a QSSM_S_* status code. */
+const char* qssm_status_string(int code);
+
+/* Rows per tile_h entry (== QSSM_TILE_ROWS), for callers that cannot read the header. */
+int qssm_tile_rows(void);
+
+/*
+ * Bytes of scratch (`ws`) that lets qssm_scan_fwd / qssm_scan_bwd /
+ * qssm_scan_aggregate_* split the time axis into parallel segments when B*D
+ * alone gives the GPU too few independent recurrences.  0 means no scratch is
+ * ever used for this shape.  Passing less (or NULL) is legal: the call then
+ * runs unsegmented.
+ * Replaces the scratch the reference allocates on every call
+ * (triton_forwards.py:152-162, triton_backwards.py:188-199).
+ */
+size_t qssm_workspace_bytes(int64_t B, int64_t L, int64_t D, int in_dtype);
+
+/* Segment count the library would pick for this shape (1 = unsegmented). */
+int qssm_auto_segments(int64_t B, int64_t L, int64_t D, int in_dtype);
+
+/*
+ * Forward scan.
+ *   c != NULL: y = c * h                       (scan(), scan_interface.py:169-213;
+ *              _TritonScanFunction.forward, :58-110; block_scan_forward_3d,
+ *              triton_forwards.py:134-172 plus the torch epilogue :104-107)
+ *   c == NULL: y = h in out_dtype              (forward_only.block_scan_forward_3d,
+ *              forward_only.py:423-540)
+ * Optional outputs
+ *   h_saved [B,L,D] fp32 contiguous: every h(t) (checkpoint=False, scan_interface.py:86,:102)
+ *   tile_h  [B, ceil(L/QSSM_TILE_ROWS), D] fp32 contiguous: h just before each
+ *           tile of QSSM_TILE_ROWS steps; lets the backward rebuild h in-kernel
+ *           (checkpoint=True, replaces the forward re-run of scan_interface.py:133-134)
+ *   h_last  [B,D] fp32: h(L-1)
+ * Optional input
+ *   h_in    [B,D] fp32: state before t=0 (sequence shards, streaming)
+ * n_seg: 0 = automatic, otherwise the number of time segments to run in parallel
+ *        (needs ws; results are identical within fp32 rounding for every value).
+ */
+int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, void* y,
+                  float* h_saved, float* tile_h, const float* h_in, float* h_last,
+                  void* ws, size_t ws_bytes,
+                  int64_t B, int64_t L, int64_t D,
+                  int64_t in_stride_b, int64_t in_stride_l,
+                  int64_t out_stride_b, int64_t out_stride_l,
+                  int in_dtype, int out_dtype, int n_seg,
+                  int* status_word, void* stream);
+
+/*
+ * Backward scan for upstream gradient dy (dtype out_dtype, strides dy_stride_*):
+ *   dh(t) = c(t)*dy(t) + a(t+1)*dh(t+1);  dx = dh*b, db = dh*x, da = dh*h(t-1), dc = dy*h
+ * Gradients are written in in_dtype into contiguous [B,L,D] buffers.
+ * Replaces _TritonScanFunction.backward (scan_interface.py:113-158) and
+ * block_scan_backward_3d (triton_backwards.py:168-209).
+ *   tile_h  (from qssm_scan_fwd) : h is rebuilt tile by tile in the kernel, or
+ *   h_saved [B,L,D] fp32         : h is read (then h_in, if the forward had one, is
+ *                                  needed again for da at t = 0).
+ *   g_in    [B,D] fp32 optional  : a(L)*dh(L) handed over by the next sequence shard
+ *   g_first [B,D] fp32 optional  : a(0)*dh(0), the value to hand to the previous shard
+ */
+int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, const void* dy,
+                  const float* h_saved, const float* tile_h, const float* h_in,
+                  const float* g_in, float* g_first,
+                  void* dx, void* da, void* db, void* dc,
+                  void* ws, size_t ws_bytes,
+                  int64_t B, int64_t L, int64_t D,
+                  int64_t in_stride_b, int64_t in_stride_l,
+                  int64_t dy_stride_b, int64_t dy_stride_l,
+                  int in_dtype, int out_dtype, int n_seg,
+                  int* status_word, void* stream);
+
+/*
+ * Aggregates of a whole [B,L,D] block, the values sequence shards exchange:
+ *   forward : A[B,D] = prod_t a(t),  H[B,D] = h(L-1) computed from h(-1)=0,
+ *             so that for any h_in  h(L-1) = A*h_in + H
+ *             (the block carry of ssm_local_forward_kernel, triton_forwards.py:33-74)
+ *   backward: P[B,D] = prod_t a(t),  Q[B,D] = a(0)*dh(0) computed from g_in=0,
+ *             so that for any g_in  g_first = P*g_in + Q
+ *             (the block carry of ssm_local_backward_kernel, triton_backwards.py:32-82)
+ */
+int qssm_scan_aggregate_fwd(const void* x, const void* a, const void* b,
+                            float* A, float* H, void* ws, size_t ws_bytes,
+                            int64_t B, int64_t L, int64_t D,
+                            int64_t in_stride_b, int64_t in_stride_l,
+                            int in_dtype, int n_seg, int* status_word, void* stream);
+
+int qssm_scan_aggregate_bwd(const void* a, const void* c, const void* dy,
+                            float* P, float* Q, void* ws, size_t ws_bytes,
+                            int64_t B, int64_t L, int64_t D,
+                            int64_t in_stride_b, int64_t in_stride_l,
+                            int64_t dy_stride_b, int64_t dy_stride_l,
+                            int in_dtype, int out_dtype, int n_seg,
+                            int* status_word, void* stream);
+
+/*
+ * Fold a list of n aggregates (A_k, H_k), each n_chan floats, stored with a
+ * stride of `stride_k` floats between consecutive k, with the scan's combine
+ *   (aL,xL) + (aR,xR) = (aR*aL, aR*xL + xR),   identity (1,0)
+ * (combine_fn, triton_forwards.py:26-30; aggregator_combine, triton_backwards.py:25-29).
+ *   reverse == 0: carry[c] = state after applying k = 0 .. upto-1 in order to seed[c]
+ *   reverse != 0: carry[c] = state after applying k = n-1 .. upto+1 (descending) to seed[c]
+ * seed may be NULL (zero).  Used to turn all-gathered shard aggregates into the
+ * h_in / g_in of shard `upto`.
+ */
+int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k,
+                    int64_t n_chan, int64_t upto, int reverse,
+                    const float* seed, float* carry, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QSSM_H */

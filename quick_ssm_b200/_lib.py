@@ -1,0 +1,239 @@
+"""ctypes binding of ``libqssm.so`` (the C ABI declared in ``include/qssm.h``).
+
+Only device pointers, sizes, strides, dtype codes and the current CUDA stream cross this
+boundary; torch is used for memory and streams, never for the arithmetic.  There is no CPU
+or eager fallback: if the library is missing, or a tensor is not on a CUDA device, the calls
+raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libqssm.so")
+
+F32, F16, BF16 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+_c_i64, _c_int, _c_vp, _c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+
+# name -> (restype, argtypes); mirrors include/qssm.h declaration by declaration
+SIGNATURES = {
+    "qssm_version": (_c_int, []),
+    "qssm_status_string": (ctypes.c_char_p, [_c_int]),
+    "qssm_tile_rows": (_c_int, []),
+    "qssm_workspace_bytes": (_c_sz, [_c_i64, _c_i64, _c_i64, _c_int]),
+    "qssm_auto_segments": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int]),
+    "qssm_scan_fwd": (_c_int, [_c_vp] * 5 + [_c_vp] * 4 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
+                      + [_c_int] * 3 + [_c_vp, _c_vp]),
+    "qssm_scan_bwd": (_c_int, [_c_vp] * 5 + [_c_vp] * 5 + [_c_vp] * 4 + [_c_vp, _c_sz] + [_c_i64] * 3
+                      + [_c_i64] * 4 + [_c_int] * 3 + [_c_vp, _c_vp]),
+    "qssm_scan_aggregate_fwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 2
+                                + [_c_int] * 2 + [_c_vp, _c_vp]),
+    "qssm_scan_aggregate_bwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
+                                + [_c_int] * 3 + [_c_vp, _c_vp]),
+    "qssm_carry_fold": (_c_int, [_c_vp, _c_vp, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_vp, _c_vp, _c_vp]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise ImportError(
+                        f"{LIB_PATH} is missing: build it with `python -m quick_ssm_b200.build` "
+                        "(nvcc, sm_100a). There is no fallback implementation.")
+                lib = ctypes.CDLL(LIB_PATH)
+                for name, (res, args) in SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.restype = res
+                    fn.argtypes = args
+                _lib = lib
+    return _lib
+
+
+def status_string(code: int) -> str:
+    return load().qssm_status_string(int(code)).decode()
+
+
+def tile_rows() -> int:
+    return int(load().qssm_tile_rows())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise TypeError(f"unsupported storage dtype {dt}; use float32, float16 or bfloat16") from None
+
+
+# ---------------------------------------------------------------------------------------------
+# device status word: pinned host memory the kernels can write, read by the host without a sync
+# ---------------------------------------------------------------------------------------------
+_status_words = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_words[key] = w
+    return w
+
+
+def check_device_status(device: Optional[torch.device] = None, synchronize: bool = False) -> None:
+    """Raise if a kernel launched earlier reported a device-side error (e.g. an expired wait)."""
+    if synchronize:
+        torch.cuda.synchronize(device)
+    words = _status_words.values() if device is None else [_status_word(torch.device(device))]
+    for w in words:
+        code = int(w[0])
+        if code != 0:
+            w.zero_()
+            raise RuntimeError(f"qssm device error {code}: {status_string(code)}")
+
+
+def _rc(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}: {status_string(code)}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if t.device.type != "cuda":
+            raise RuntimeError("the qssm kernels need CUDA tensors; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("all tensors must live on the same CUDA device")
+    return dev
+
+
+def _blds(t: torch.Tensor) -> Tuple[int, int]:
+    """(stride_b, stride_l) in elements of a [B, L, D] tensor whose D stride is 1."""
+    return int(t.stride(0)), int(t.stride(1))
+
+
+def layout_ok(t: torch.Tensor) -> bool:
+    """Can the kernels address this [B, L, D] view in place?"""
+    B, L, D = t.shape
+    if B * L * D == 0:
+        return True
+    return (D == 1 or t.stride(2) == 1) and (L == 1 or t.stride(1) >= D) and (B == 1 or t.stride(0) >= D)
+
+
+def same_layout(*ts: torch.Tensor) -> bool:
+    s0 = ts[0].stride()
+    return all(t.stride() == s0 for t in ts[1:])
+
+
+def workspace(B: int, L: int, D: int, code: int, n_seg: int, device) -> Optional[torch.Tensor]:
+    lib = load()
+    if n_seg and n_seg > 1:
+        nbytes = 3 * B * n_seg * D * 4
+    else:
+        nbytes = int(lib.qssm_workspace_bytes(B, L, D, code))
+    if nbytes == 0:
+        return None
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+# ---------------------------------------------------------------------------------------------
+# thin call wrappers (arguments already validated / laid out by the caller)
+# ---------------------------------------------------------------------------------------------
+def scan_fwd(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None, n_seg: int = 0) -> None:
+    dev = _require_cuda(x, a, b, c, y, h_saved, tile_h, h_in, h_last)
+    B, L, D = x.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        code_in, code_out = dtype_code(x.dtype), dtype_code(y.dtype)
+        ws = workspace(B, L, D, code_in, n_seg, dev)
+        sb, sl = _blds(x)
+        ob, ol = _blds(y)
+        rc = load().qssm_scan_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(y), _ptr(h_saved), _ptr(tile_h),
+                                  _ptr(h_in), _ptr(h_last), _ptr(ws), 0 if ws is None else ws.numel(),
+                                  B, L, D, sb, sl, ob, ol, code_in, code_out, int(n_seg),
+                                  _status_word(dev).data_ptr(), _stream(dev))
+    _rc(rc, "qssm_scan_fwd")
+
+
+def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=None, g_in=None, g_first=None,
+             n_seg: int = 0) -> None:
+    dev = _require_cuda(x, a, b, c, dy, dx, da, db, dc, h_saved, tile_h, h_in, g_in, g_first)
+    B, L, D = x.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        code_in, code_out = dtype_code(x.dtype), dtype_code(dy.dtype)
+        ws = workspace(B, L, D, code_in, n_seg, dev)
+        sb, sl = _blds(x)
+        gb, gl = _blds(dy)
+        rc = load().qssm_scan_bwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(dy), _ptr(h_saved), _ptr(tile_h),
+                                  _ptr(h_in), _ptr(g_in), _ptr(g_first), _ptr(dx), _ptr(da), _ptr(db), _ptr(dc),
+                                  _ptr(ws), 0 if ws is None else ws.numel(), B, L, D, sb, sl, gb, gl,
+                                  code_in, code_out, int(n_seg), _status_word(dev).data_ptr(), _stream(dev))
+    _rc(rc, "qssm_scan_bwd")
+
+
+def aggregate_fwd(x, a, b, A, H, *, n_seg: int = 0) -> None:
+    dev = _require_cuda(x, a, b, A, H)
+    B, L, D = x.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        code = dtype_code(x.dtype)
+        ws = workspace(B, L, D, code, n_seg, dev)
+        sb, sl = _blds(x)
+        rc = load().qssm_scan_aggregate_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(A), _ptr(H), _ptr(ws),
+                                            0 if ws is None else ws.numel(), B, L, D, sb, sl, code, int(n_seg),
+                                            _status_word(dev).data_ptr(), _stream(dev))
+    _rc(rc, "qssm_scan_aggregate_fwd")
+
+
+def aggregate_bwd(a, c, dy, P, Q, *, n_seg: int = 0) -> None:
+    dev = _require_cuda(a, c, dy, P, Q)
+    B, L, D = a.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        code, code_dy = dtype_code(a.dtype), dtype_code(dy.dtype)
+        ws = workspace(B, L, D, code, n_seg, dev)
+        sb, sl = _blds(a)
+        gb, gl = _blds(dy)
+        rc = load().qssm_scan_aggregate_bwd(_ptr(a), _ptr(c), _ptr(dy), _ptr(P), _ptr(Q), _ptr(ws),
+                                            0 if ws is None else ws.numel(), B, L, D, sb, sl, gb, gl, code, code_dy,
+                                            int(n_seg), _status_word(dev).data_ptr(), _stream(dev))
+    _rc(rc, "qssm_scan_aggregate_bwd")
+
+
+def carry_fold(A, H, upto: int, *, reverse: bool, seed=None) -> torch.Tensor:
+    """A, H: [n, ...] fp32 contiguous stacks of aggregates; returns the carry entering slot ``upto``."""
+    dev = _require_cuda(A, H, seed)
+    n = A.shape[0]
+    n_chan = A[0].numel() if n > 0 else (seed.numel() if seed is not None else 0)
+    out = torch.empty(A.shape[1:], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = load().qssm_carry_fold(_ptr(A), _ptr(H), n, int(A.stride(0)) if n > 0 else n_chan, n_chan, int(upto),
+                                    1 if reverse else 0, _ptr(seed), _ptr(out), _stream(dev))
+    _rc(rc, "qssm_carry_fold")
+    return out

@@ -1,0 +1,1256 @@
+// Gated linear scan for NVIDIA B200 (sm_100a):  h(t) = a(t) h(t-1) + b(t) x(t),  y(t) = c(t) h(t).
+//
+// Execution model
+// ---------------
+// The path is HBM-bound (about three fused multiply-adds per element, no
+// contraction), so the kernels are built around keeping many bytes in flight
+// with the bulk tensor copy engine (TMA) and touching every tensor once:
+//
+//  * one warp owns one "chain": a 128-byte-wide column strip of one batch
+//    entry (32 lanes x one 4-byte word: 32 fp32 or 64 fp16/bf16 channels) over
+//    a range of time steps, and walks it sequentially in tiles of TT rows;
+//  * lane 0 issues cp.async.bulk.tensor loads of the next tiles of every input
+//    into a ring of shared-memory stages (completion on an mbarrier per
+//    stage); the warp scans the current tile out of shared memory with fp32
+//    state in registers, writes results back to shared memory and lane 0
+//    issues the bulk tensor store.  One CTA == one warp, so no CTA-wide
+//    barrier exists anywhere; many small CTAs per SM give the ring depth;
+//  * the carry between tiles of a chain never leaves registers.  When B*D
+//    alone gives too few chains to fill the GPU the time axis is cut into
+//    segments: an aggregate kernel (reads only the tensors the carry depends
+//    on) produces (prod a, local end state) per segment, a tiny kernel scans
+//    those per channel, and the main kernel runs every segment seeded.  The
+//    same aggregate/seed pair is what sequence shards on different GPUs
+//    exchange.
+//  * shapes the copy engine cannot address (row pitch or base not a multiple
+//    of 16 bytes, e.g. D = 1) take the same kernels with guarded per-lane
+//    loads and stores instead of bulk copies.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel records
+// QSSM_S_TMA_TIMEOUT in the caller's status word and leaves.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/qssm.h"
+
+namespace {
+
+constexpr int TT = QSSM_TILE_ROWS;  // rows per tile
+constexpr int ROW_BYTES = 128;      // bytes of one input row strip (32 lanes x 4 B)
+constexpr int MAX_STAGES = 12;
+
+// ---------------------------------------------------------------------------------------------
+// element helpers
+// ---------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// V consecutive channels of one lane, moved with a single shared-memory access.
+template <typename T, int V> struct alignas(sizeof(T) * V) Vec { T v[V]; };
+
+// Row r of a tile whose rows hold 32 lanes x V elements of T.
+template <typename T, int V>
+__device__ __forceinline__ void tile_read(const unsigned char* tile, int r, int lane, float (&out)[V]) {
+    const Vec<T, V> w = reinterpret_cast<const Vec<T, V>*>(tile)[r * 32 + lane];
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = to_f<T>(w.v[i]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void tile_write(unsigned char* tile, int r, int lane, const float (&in)[V]) {
+    Vec<T, V> w;
+#pragma unroll
+    for (int i = 0; i < V; ++i) w.v[i] = from_f<T>(in[i]);
+    reinterpret_cast<Vec<T, V>*>(tile)[r * 32 + lane] = w;
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers: mbarrier, bulk tensor copies
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after about two seconds.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 16) __nanosleep(32);
+        if ((it & 1023u) == 1023u && global_timer_ns() - t0 > 2000000000ull) return false;
+        if (it > (1u << 28)) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+// kernel parameters
+// ---------------------------------------------------------------------------------------------
+struct alignas(64) TensorDesc {
+    CUtensorMap map;     // bulk-copy path
+    void* ptr;           // guarded path
+    long long stride_b;  // elements
+    long long stride_l;  // elements
+    long long reserved;
+};
+
+struct Geom {
+    long long B, L, D;
+    int n_dtiles;   // ceil(D / channels per warp)
+    int n_seg;      // time segments
+    int seg_rows;   // rows per segment, a multiple of TT
+    int n_stages;   // ring depth
+    int use_tma;    // 0: guarded per-lane accesses
+    int* status;    // may be NULL
+};
+
+struct FwdParams {
+    TensorDesc x, a, b, c, y, hs;
+    float* tile_h;       // [B, ceil(L/TT), D] or NULL
+    const float* h_in;   // [B, n_seg, D] or NULL
+    float* h_last;       // [B, D] or NULL
+    Geom g;
+};
+
+struct BwdParams {
+    TensorDesc x, a, b, c, dy, hsrc;  // hsrc: tile_h (recompute) or h_saved
+    TensorDesc dx, da, db, dc;
+    const float* h_in;   // [B, D] or NULL (only read with h_saved, for da at t = 0)
+    const float* g_in;   // [B, n_seg, D] or NULL
+    float* g_first;      // [B, D] or NULL
+    Geom g;
+};
+
+struct AggParams {
+    TensorDesc t0, t1, t2;  // forward: x, a, b; backward: a, c, dy
+    float* A;               // [B, n_seg, D]
+    float* H;               // [B, n_seg, D]
+    Geom g;
+};
+
+__device__ __forceinline__ void report(int* status, int code) {
+    if (status != nullptr) {
+        *reinterpret_cast<volatile int*>(status) = code;
+        __threadfence_system();
+    }
+}
+
+// Guarded fill of one tile (rows t0 .. t0+TT-1, this lane's V channels) with zero padding.
+template <typename T, int V>
+__device__ __forceinline__ void plain_fill(unsigned char* tile, const TensorDesc& td, long long b, long long t0,
+                                           long long t_lim, long long d_lane, long long D, int lane) {
+    const T* base = reinterpret_cast<const T*>(td.ptr) + b * td.stride_b;
+#pragma unroll 4
+    for (int r = 0; r < TT; ++r) {
+        Vec<T, V> w;
+        const long long t = t0 + r;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const bool ok = (t >= 0) && (t < t_lim) && (d_lane + i < D);
+            w.v[i] = ok ? base[t * td.stride_l + d_lane + i] : from_f<T>(0.f);
+        }
+        reinterpret_cast<Vec<T, V>*>(tile)[r * 32 + lane] = w;
+    }
+}
+// Guarded write-back of one tile.
+template <typename T, int V>
+__device__ __forceinline__ void plain_drain(const unsigned char* tile, const TensorDesc& td, long long b,
+                                            long long t0, long long t_lim, long long d_lane, long long D,
+                                            int lane) {
+    T* base = reinterpret_cast<T*>(td.ptr) + b * td.stride_b;
+#pragma unroll 4
+    for (int r = 0; r < TT; ++r) {
+        const Vec<T, V> w = reinterpret_cast<const Vec<T, V>*>(tile)[r * 32 + lane];
+        const long long t = t0 + r;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (t < t_lim && d_lane + i < D) base[t * td.stride_l + d_lane + i] = w.v[i];
+    }
+}
+
+// Chain coordinates of this warp.
+struct Chain {
+    long long b, d0, t_begin, t_end;
+    int seg, n_tiles;
+    bool empty;
+};
+__device__ __forceinline__ Chain chain_of_block(const Geom& g, int chans_per_warp) {
+    Chain c;
+    const long long id = blockIdx.x;
+    const long long dt = id % g.n_dtiles;
+    const long long rest = id / g.n_dtiles;
+    c.seg = static_cast<int>(rest % g.n_seg);
+    c.b = rest / g.n_seg;
+    c.d0 = dt * chans_per_warp;
+    c.t_begin = static_cast<long long>(c.seg) * g.seg_rows;
+    c.t_end = c.t_begin + g.seg_rows;
+    if (c.t_end > g.L) c.t_end = g.L;
+    c.empty = c.t_begin >= c.t_end;
+    c.n_tiles = c.empty ? 0 : static_cast<int>((c.t_end - c.t_begin + TT - 1) / TT);
+    return c;
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward:  y = c*h (HAS_C) or y = h; optional fp32 h, optional tile boundary states
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, bool HAS_C, bool SAVE_H>
+__global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ FwdParams p) {
+    constexpr int V = 4 / sizeof(Tin);
+    constexpr int DT = 32 * V;
+    constexpr int NIN = HAS_C ? 4 : 3;
+    constexpr int IN_TILE = TT * ROW_BYTES;
+    constexpr int OUT_TILE = TT * 32 * V * (int)sizeof(Tout);
+    constexpr int HS_TILE = SAVE_H ? TT * 32 * V * 4 : 0;
+    constexpr int STAGE = NIN * IN_TILE;
+    constexpr int OUTBUF = OUT_TILE + HS_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    unsigned char* const stages = smem;
+    unsigned char* const outbuf = smem + (size_t)NS * STAGE;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(outbuf + 2 * OUTBUF);
+
+    const int lane = threadIdx.x;
+    const Chain ch = chain_of_block(g, DT);
+    if (ch.empty) return;
+    const long long d_lane = ch.d0 + (long long)lane * V;
+    const bool tma = g.use_tma != 0;
+
+    float h[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) h[i] = 0.f;
+    if (p.h_in != nullptr) {
+        const float* src = p.h_in + (ch.b * g.n_seg + ch.seg) * g.D;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) h[i] = src[d_lane + i];
+    }
+
+    if (tma) {
+        if (lane == 0) {
+            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+
+    const int c0 = (int)ch.d0, c2 = (int)ch.b;
+    auto issue = [&](int j) {  // lane 0 only: loads of tile j into stage j % NS
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        const int row = (int)(ch.t_begin + (long long)j * TT);
+        fence_proxy_async();
+        mbar_expect_tx(&bars[s], STAGE);
+        tma_load_3d(st + 0 * IN_TILE, &p.x.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.a.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.b.map, &bars[s], c0, row, c2);
+        if (HAS_C) tma_load_3d(st + 3 * IN_TILE, &p.c.map, &bars[s], c0, row, c2);
+    };
+
+    if (tma && lane == 0) {
+        const int pre = ch.n_tiles < NS - 1 ? ch.n_tiles : NS - 1;
+        for (int j = 0; j < pre; ++j) issue(j);
+    }
+
+    bool ok = true;
+    for (int j = 0; j < ch.n_tiles; ++j) {
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        unsigned char* ob = outbuf + (size_t)(j & 1) * OUTBUF;
+        const long long t0 = ch.t_begin + (long long)j * TT;
+        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+
+        if (tma) {
+            if (lane == 0 && j + NS - 1 < ch.n_tiles) issue(j + NS - 1);
+            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            // the store issued two tiles ago must have finished reading this output buffer
+            if (lane == 0) tma_wait_read<1>();
+            __syncwarp();
+        } else {
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            if (HAS_C) plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+        }
+
+        if (p.tile_h != nullptr) {
+            float* dst = p.tile_h + (ch.b * ((g.L + TT - 1) / TT) + t0 / TT) * g.D;
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                if (d_lane + i < g.D) dst[d_lane + i] = h[i];
+        }
+
+#pragma unroll
+        for (int r = 0; r < TT; ++r) {
+            float xv[V], av[V], bv[V], yv[V];
+            tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
+            tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
+            tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
+            if (r < nrows) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) h[i] = fmaf(av[i], h[i], bv[i] * xv[i]);
+            }
+            if (HAS_C) {
+                float cv[V];
+                tile_read<Tin, V>(st + 3 * IN_TILE, r, lane, cv);
+#pragma unroll
+                for (int i = 0; i < V; ++i) yv[i] = cv[i] * h[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) yv[i] = h[i];
+            }
+            tile_write<Tout, V>(ob, r, lane, yv);
+            if (SAVE_H) tile_write<float, V>(ob + OUT_TILE, r, lane, h);
+        }
+
+        if (tma) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&p.y.map, ob, c0, (int)t0, c2);
+                if (SAVE_H) tma_store_3d(&p.hs.map, ob + OUT_TILE, c0, (int)t0, c2);
+                tma_commit();
+            }
+        } else {
+            plain_drain<Tout, V>(ob, p.y, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            if (SAVE_H) plain_drain<float, V>(ob + OUT_TILE, p.hs, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+        }
+        __syncwarp();
+    }
+
+    if (tma && lane == 0) tma_wait_all();
+    if (!ok) {
+        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
+        return;
+    }
+    if (p.h_last != nullptr && ch.seg == g.n_seg - 1) {
+        float* dst = p.h_last + ch.b * g.D;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) dst[d_lane + i] = h[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward: reverse scan of dh with h rebuilt per tile (tile_h) or read (h_saved)
+// The carry between tiles is G(t) = a(t) * dh(t), so no halo row of `a` is needed.
+// Gradients overwrite the shared-memory slots of x, a, b, c and are stored from there.
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, typename Tdy, bool SAVED_H>
+__global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ BwdParams p) {
+    constexpr int V = 4 / sizeof(Tin);
+    constexpr int DT = 32 * V;
+    constexpr int IN_TILE = TT * ROW_BYTES;
+    constexpr int DY_TILE = TT * 32 * V * (int)sizeof(Tdy);
+    constexpr int HROW = 32 * V * 4;                           // one fp32 row
+    constexpr int H_TILE = SAVED_H ? (TT + 1) * HROW : HROW;   // rows t0-1 .. t0+TT-1, or the boundary row
+    constexpr int STAGE = 4 * IN_TILE + DY_TILE + ((H_TILE + 127) / 128) * 128;
+    constexpr int OFF_DY = 4 * IN_TILE;
+    constexpr int OFF_H = OFF_DY + DY_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    unsigned char* const stages = smem;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + (size_t)NS * STAGE);
+
+    const int lane = threadIdx.x;
+    const Chain ch = chain_of_block(g, DT);
+    if (ch.empty) return;
+    const long long d_lane = ch.d0 + (long long)lane * V;
+    const bool tma = g.use_tma != 0;
+    const long long tiles_per_b = (g.L + TT - 1) / TT;
+
+    float G[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) G[i] = 0.f;
+    if (p.g_in != nullptr) {
+        const float* src = p.g_in + (ch.b * g.n_seg + ch.seg) * g.D;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) G[i] = src[d_lane + i];
+    }
+
+    if (tma) {
+        if (lane == 0) {
+            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+
+    const int c0 = (int)ch.d0, c2 = (int)ch.b;
+    // processing order j = 0 .. n_tiles-1 walks the tiles from the last to the first
+    auto tile_row = [&](int j) { return ch.t_begin + (long long)(ch.n_tiles - 1 - j) * TT; };
+    auto issue = [&](int j) {
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        const int row = (int)tile_row(j);
+        fence_proxy_async();
+        mbar_expect_tx(&bars[s], 4 * IN_TILE + DY_TILE + H_TILE);
+        tma_load_3d(st + 0 * IN_TILE, &p.x.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.a.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.b.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 3 * IN_TILE, &p.c.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + OFF_DY, &p.dy.map, &bars[s], c0, row, c2);
+        if (SAVED_H)
+            tma_load_3d(st + OFF_H, &p.hsrc.map, &bars[s], c0, row - 1, c2);  // row -1 reads zero fill
+        else
+            tma_load_3d(st + OFF_H, &p.hsrc.map, &bars[s], c0, row / TT, c2);
+    };
+
+    // Gradients are stored from the stage itself, so a stage can be refilled only after the store
+    // issued from it has finished reading: prefetch distance is NS - 2.
+    const int PF = NS - 2;
+    if (tma && lane == 0) {
+        const int pre = ch.n_tiles < PF ? ch.n_tiles : PF;
+        for (int j = 0; j < pre; ++j) issue(j);
+    }
+
+    bool ok = true;
+    for (int j = 0; j < ch.n_tiles; ++j) {
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        const long long t0 = tile_row(j);
+        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+
+        if (tma) {
+            if (lane == 0 && j + PF < ch.n_tiles) {
+                tma_wait_read<1>();  // the store of tile j-2 (stage (j+PF) % NS) is done with its slots
+                issue(j + PF);
+            }
+            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+        } else {
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tdy, V>(st + OFF_DY, p.dy, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            const float* hb = reinterpret_cast<const float*>(p.hsrc.ptr);
+            if (SAVED_H) {
+                for (int r = 0; r <= TT; ++r) {
+                    float w[V];
+                    const long long t = t0 - 1 + r;
+#pragma unroll
+                    for (int i = 0; i < V; ++i)
+                        w[i] = (t >= 0 && t < ch.t_end && d_lane + i < g.D)
+                                   ? hb[ch.b * p.hsrc.stride_b + t * p.hsrc.stride_l + d_lane + i]
+                                   : 0.f;
+                    tile_write<float, V>(st + OFF_H, r, lane, w);
+                }
+            } else {
+                float w[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i)
+                    w[i] = (d_lane + i < g.D) ? hb[(ch.b * tiles_per_b + t0 / TT) * g.D + d_lane + i] : 0.f;
+                tile_write<float, V>(st + OFF_H, 0, lane, w);
+            }
+        }
+
+        // h(t0-1 .. t0+TT-1): row 0 of hreg is the state before the tile
+        float hreg[TT + 1][V];
+        if (SAVED_H) {
+#pragma unroll
+            for (int r = 0; r <= TT; ++r) tile_read<float, V>(st + OFF_H, r, lane, hreg[r]);
+            if (t0 == 0 && p.h_in != nullptr) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) hreg[0][i] = (d_lane + i < g.D) ? p.h_in[ch.b * g.D + d_lane + i] : 0.f;
+            }
+        } else {
+            tile_read<float, V>(st + OFF_H, 0, lane, hreg[0]);
+#pragma unroll
+            for (int r = 0; r < TT; ++r) {
+                float xv[V], av[V], bv[V];
+                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
+                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
+                tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
+#pragma unroll
+                for (int i = 0; i < V; ++i) hreg[r + 1][i] = fmaf(av[i], hreg[r][i], bv[i] * xv[i]);
+            }
+        }
+
+#pragma unroll
+        for (int r = TT - 1; r >= 0; --r) {
+            float xv[V], av[V], bv[V], cv[V], gy[V];
+            tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
+            tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
+            tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
+            tile_read<Tin, V>(st + 3 * IN_TILE, r, lane, cv);
+            tile_read<Tdy, V>(st + OFF_DY, r, lane, gy);
+            float dxv[V], dav[V], dbv[V], dcv[V];
+            const bool live = r < nrows;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float dh = fmaf(cv[i], gy[i], G[i]);
+                dxv[i] = dh * bv[i];
+                dbv[i] = dh * xv[i];
+                dav[i] = dh * hreg[r][i];
+                dcv[i] = gy[i] * hreg[r + 1][i];
+                if (live) G[i] = av[i] * dh;
+            }
+            tile_write<Tin, V>(st + 0 * IN_TILE, r, lane, dxv);
+            tile_write<Tin, V>(st + 1 * IN_TILE, r, lane, dav);
+            tile_write<Tin, V>(st + 2 * IN_TILE, r, lane, dbv);
+            tile_write<Tin, V>(st + 3 * IN_TILE, r, lane, dcv);
+        }
+
+        if (tma) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(&p.dx.map, st + 0 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.da.map, st + 1 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.db.map, st + 2 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.dc.map, st + 3 * IN_TILE, c0, (int)t0, c2);
+                tma_commit();
+            }
+        } else {
+            plain_drain<Tin, V>(st + 0 * IN_TILE, p.dx, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 1 * IN_TILE, p.da, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 2 * IN_TILE, p.db, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 3 * IN_TILE, p.dc, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+        }
+        __syncwarp();
+    }
+
+    if (tma && lane == 0) tma_wait_all();
+    if (!ok) {
+        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
+        return;
+    }
+    if (p.g_first != nullptr && ch.seg == 0) {
+        float* dst = p.g_first + ch.b * g.D;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) dst[d_lane + i] = G[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// aggregates of a segment.  forward: (prod a, h_end from 0) from x, a, b
+//                           backward: (prod a, a(t0) dh(t0) from 0) from a, c, dy
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, typename Tdy, bool REVERSE>
+__global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ AggParams p) {
+    constexpr int V = 4 / sizeof(Tin);
+    constexpr int DT = 32 * V;
+    constexpr int IN_TILE = TT * ROW_BYTES;
+    constexpr int T2_TILE = REVERSE ? TT * 32 * V * (int)sizeof(Tdy) : IN_TILE;
+    constexpr int STAGE = 2 * IN_TILE + T2_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    unsigned char* const stages = smem;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + (size_t)NS * STAGE);
+
+    const int lane = threadIdx.x;
+    const Chain ch = chain_of_block(g, DT);
+    const long long d_lane = ch.d0 + (long long)lane * V;
+    float* const outA = p.A + (ch.b * g.n_seg + ch.seg) * g.D;
+    float* const outH = p.H + (ch.b * g.n_seg + ch.seg) * g.D;
+    if (ch.empty) {  // identity
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) { outA[d_lane + i] = 1.f; outH[d_lane + i] = 0.f; }
+        return;
+    }
+    const bool tma = g.use_tma != 0;
+
+    float A[V], H[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { A[i] = 1.f; H[i] = 0.f; }
+
+    if (tma) {
+        if (lane == 0) {
+            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+    const int c0 = (int)ch.d0, c2 = (int)ch.b;
+    auto tile_row = [&](int j) {
+        return ch.t_begin + (long long)(REVERSE ? ch.n_tiles - 1 - j : j) * TT;
+    };
+    auto issue = [&](int j) {
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        const int row = (int)tile_row(j);
+        fence_proxy_async();
+        mbar_expect_tx(&bars[s], STAGE);
+        tma_load_3d(st + 0 * IN_TILE, &p.t0.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.t1.map, &bars[s], c0, row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.t2.map, &bars[s], c0, row, c2);
+    };
+    if (tma && lane == 0) {
+        const int pre = ch.n_tiles < NS - 1 ? ch.n_tiles : NS - 1;
+        for (int j = 0; j < pre; ++j) issue(j);
+    }
+    bool ok = true;
+    for (int j = 0; j < ch.n_tiles; ++j) {
+        const int s = j % NS;
+        unsigned char* st = stages + (size_t)s * STAGE;
+        const long long t0 = tile_row(j);
+        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+        if (tma) {
+            if (lane == 0 && j + NS - 1 < ch.n_tiles) issue(j + NS - 1);
+            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+        } else {
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.t0, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.t1, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            if (REVERSE)
+                plain_fill<Tdy, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            else
+                plain_fill<Tin, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+        }
+        if (!REVERSE) {
+#pragma unroll
+            for (int r = 0; r < TT; ++r) {
+                float xv[V], av[V], bv[V];
+                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
+                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
+                tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
+                if (r < nrows) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) { A[i] *= av[i]; H[i] = fmaf(av[i], H[i], bv[i] * xv[i]); }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = TT - 1; r >= 0; --r) {
+                float av[V], cv[V], gy[V];
+                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, av);
+                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, cv);
+                tile_read<Tdy, V>(st + 2 * IN_TILE, r, lane, gy);
+                if (r < nrows) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) { A[i] *= av[i]; H[i] = av[i] * fmaf(cv[i], gy[i], H[i]); }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    if (!ok) {
+        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+        if (d_lane + i < g.D) { outA[d_lane + i] = A[i]; outH[d_lane + i] = H[i]; }
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-channel scan of segment aggregates -> seeds of every segment (+ optional totals)
+//   A, H: [B, n_seg, D];  seed: [B, D] or NULL;  out: [B, n_seg, D];  totA/totH: [B, D] or NULL
+// ---------------------------------------------------------------------------------------------
+__global__ void seg_carry_kernel(const float* __restrict__ A, const float* __restrict__ H,
+                                 const float* __restrict__ seed, float* __restrict__ out,
+                                 float* __restrict__ totA, float* __restrict__ totH, long long B, int n_seg,
+                                 long long D, int reverse) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= B * D) return;
+    const long long b = idx / D, d = idx % D;
+    float run = seed != nullptr ? seed[idx] : 0.f;
+    float pa = 1.f, ph = 0.f;
+    for (int k = 0; k < n_seg; ++k) {
+        const int s = reverse ? n_seg - 1 - k : k;
+        const long long o = (b * n_seg + s) * D + d;
+        const float av = A[o], hv = H[o];
+        if (out != nullptr) out[o] = run;
+        run = fmaf(av, run, hv);
+        ph = fmaf(av, ph, hv);
+        pa *= av;
+    }
+    if (totA != nullptr) totA[idx] = pa;
+    if (totH != nullptr) totH[idx] = ph;
+}
+
+__global__ void carry_fold_kernel(const float* __restrict__ A, const float* __restrict__ H, long long n,
+                                  long long stride_k, long long n_chan, long long upto, int reverse,
+                                  const float* __restrict__ seed, float* __restrict__ carry) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_chan) return;
+    float run = seed != nullptr ? seed[idx] : 0.f;
+    if (!reverse) {
+        for (long long k = 0; k < upto; ++k) run = fmaf(A[k * stride_k + idx], run, H[k * stride_k + idx]);
+    } else {
+        for (long long k = n - 1; k > upto; --k) run = fmaf(A[k * stride_k + idx], run, H[k * stride_k + idx]);
+    }
+    carry[idx] = run;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Driver-API calls (tensor map encoding) need the primary context current on the calling thread;
+// a thread that has only inherited a device ordinal (e.g. an autograd worker) may not have one yet.
+void ensure_context() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+}
+
+int dtype_size(int dt) { return dt == QSSM_F32 ? 4 : (dt == QSSM_F16 || dt == QSSM_BF16) ? 2 : 0; }
+
+CUtensorMapDataType tm_dtype(int dt) {
+    return dt == QSSM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                          : dt == QSSM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
+// Can the copy engine address a [B, L, D] view with these strides?
+bool tma_ok(const void* ptr, long long B, long long L, long long D, long long sb, long long sl, int esize) {
+    if (ptr == nullptr) return true;
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return false;
+    if ((sl * esize) % 16 != 0 || (B > 1 && (sb * esize) % 16 != 0)) return false;
+    if (sl * esize >= (1ll << 40) || sb * esize >= (1ll << 40)) return false;
+    if (D >= (1ll << 32) || L >= (1ll << 31) || B >= (1ll << 31)) return false;
+    return true;
+}
+
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+}
+
+// dims (D, rows, B); box (box_d, box_rows, 1)
+int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long rows, long long D, long long sb,
+              long long sl, int box_d, int box_rows, bool use_tma) {
+    memset(&td, 0, sizeof(td));
+    td.ptr = const_cast<void*>(ptr);
+    td.stride_b = sb;
+    td.stride_l = sl;
+    if (!use_tma || ptr == nullptr) return 0;
+    static thread_local bool have_context = false;
+    if (!have_context) {
+        ensure_context();
+        have_context = true;
+    }
+    EncodeTiledFn enc = encode_fn();
+    if (enc == nullptr) return QSSM_E_DRIVER;
+    const int es = dtype_size(dt);
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)B};
+    long long sb_bytes = sb * es;
+    if (B <= 1 || sb_bytes == 0) sb_bytes = ((rows * sl * es + 15) / 16) * 16;
+    if (sb_bytes == 0) sb_bytes = 16;
+    cuuint64_t strides[2] = {(cuuint64_t)(sl * es), (cuuint64_t)sb_bytes};
+    cuuint32_t box[3] = {(cuuint32_t)box_d, (cuuint32_t)box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(&td.map, tm_dtype(dt), 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS && env_int("QSSM_DEBUG", 0) != 0)
+        fprintf(stderr,
+                "qssm: cuTensorMapEncodeTiled failed (%d): ptr=%p dt=%d dims=(%llu,%llu,%llu) strides=(%llu,%llu) "
+                "box=(%u,%u,%u)\n",
+                (int)r, ptr, dt, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box[0],
+                box[1], box[2]);
+    return r == CUDA_SUCCESS ? 0 : QSSM_E_STRIDE;
+}
+
+
+int sm_count() {
+    static int n = []() {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        return v;
+    }();
+    return n;
+}
+
+long long n_chains(long long B, long long D, int in_dtype) {
+    const int chans = ROW_BYTES / dtype_size(in_dtype);
+    return B * ((D + chans - 1) / chans);
+}
+
+// Segment count: split time only when batch x channels gives fewer chains than SMs.
+int auto_segments(long long B, long long L, long long D, int in_dtype) {
+    if (B <= 0 || L <= 0 || D <= 0 || dtype_size(in_dtype) == 0) return 1;
+    const long long chains = n_chains(B, D, in_dtype);
+    if (chains >= 128) return 1;
+    long long want = (512 + chains - 1) / chains;
+    const long long max_by_len = L / (8 * TT);  // at least 8 tiles per segment
+    if (want > max_by_len) want = max_by_len;
+    if (want < 1) want = 1;
+    if (want > 4096) want = 4096;
+    return (int)want;
+}
+
+size_t ws_bytes_for(long long B, long long D, int n_seg) {
+    if (n_seg <= 1) return 0;
+    return (size_t)3 * (size_t)B * (size_t)n_seg * (size_t)D * sizeof(float);
+}
+
+// Ring depth: spread the shared memory of an SM over the chains expected to be resident on it.
+int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int prefetch_slack) {
+    int forced = env_int("QSSM_STAGES", 0);
+    long long per_sm = (chains_total + sm_count() - 1) / sm_count();
+    int max_res = env_int("QSSM_RESIDENT", 6);
+    if (per_sm > max_res) per_sm = max_res;
+    if (per_sm < 1) per_sm = 1;
+    const int budget = (int)((227 * 1024) / per_sm) - 1024 - fixed_bytes - MAX_STAGES * 8 - 128;
+    int ns = budget / stage_bytes;
+    if (forced > 0) ns = forced;
+    const int lo = 2 + prefetch_slack;
+    if (ns < lo) ns = lo;
+    if (ns > MAX_STAGES) ns = MAX_STAGES;
+    while (ns > lo && ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 128 > 227 * 1024) --ns;
+    return ns;
+}
+
+struct Plan {
+    Geom g;
+    long long chains;  // grid size
+};
+
+int make_plan(Plan& pl, long long B, long long L, long long D, int in_dtype, int n_seg, int* status) {
+    const int chans = ROW_BYTES / dtype_size(in_dtype);
+    Geom& g = pl.g;
+    g.B = B; g.L = L; g.D = D;
+    g.n_dtiles = (int)((D + chans - 1) / chans);
+    if (n_seg < 1) n_seg = 1;
+    long long seg_rows = (L + n_seg - 1) / n_seg;
+    seg_rows = ((seg_rows + TT - 1) / TT) * TT;
+    n_seg = (int)((L + seg_rows - 1) / seg_rows);
+    g.n_seg = n_seg;
+    g.seg_rows = (int)seg_rows;
+    g.status = status;
+    g.use_tma = 1;
+    g.n_stages = 2;
+    pl.chains = B * n_seg * g.n_dtiles;
+    if (pl.chains > 0x7fffffffll) return QSSM_E_SHAPE;
+    return 0;
+}
+
+template <typename K, typename P>
+int launch(K kernel, const P& params, long long grid, int smem_bytes, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<(unsigned)grid, 32, smem_bytes, stream>>>(params);
+    e = cudaGetLastError();
+    return (int)e;
+}
+
+int check_common(long long B, long long L, long long D, int in_dtype, int out_dtype) {
+    if (B < 0 || L < 0 || D < 0) return QSSM_E_SHAPE;
+    if (dtype_size(in_dtype) == 0 || dtype_size(out_dtype) == 0) return QSSM_E_DTYPE;
+    if (!(out_dtype == in_dtype || out_dtype == QSSM_F32)) return QSSM_E_DTYPE;
+    if (L >= (1ll << 31) || B >= (1ll << 31)) return QSSM_E_SHAPE;
+    return 0;
+}
+int check_strides(long long L, long long D, long long sb, long long sl) {
+    if (sl < D) return QSSM_E_STRIDE;
+    if (sb < 0) return QSSM_E_STRIDE;
+    (void)L;
+    return 0;
+}
+
+// dispatch on (in dtype, out dtype): out is the in dtype or fp32
+#define QSSM_DISPATCH(in_dt, out_dt, BODY)                                                     \
+    do {                                                                                       \
+        if ((in_dt) == QSSM_F32) { using Tin = float; using Tout = float; BODY; }              \
+        else if ((in_dt) == QSSM_F16 && (out_dt) == QSSM_F16) { using Tin = __half; using Tout = __half; BODY; } \
+        else if ((in_dt) == QSSM_F16) { using Tin = __half; using Tout = float; BODY; }        \
+        else if ((in_dt) == QSSM_BF16 && (out_dt) == QSSM_BF16) { using Tin = __nv_bfloat16; using Tout = __nv_bfloat16; BODY; } \
+        else { using Tin = __nv_bfloat16; using Tout = float; BODY; }                          \
+    } while (0)
+
+// segment aggregates -> seeds.  A/H/seeds live in ws: three [B, n_seg, D] fp32 arrays.
+struct SegScratch {
+    float *A, *H, *seeds;
+};
+SegScratch carve(void* ws, long long B, int n_seg, long long D) {
+    SegScratch s;
+    const size_t n = (size_t)B * n_seg * D;
+    s.A = reinterpret_cast<float*>(ws);
+    s.H = s.A + n;
+    s.seeds = s.H + n;
+    return s;
+}
+
+int run_aggregate(bool reverse, const void* t0, const void* t1, const void* t2, float* A, float* H,
+                  const Plan& pl, long long sb, long long sl, long long sb2, long long sl2, int in_dtype,
+                  int dt2, cudaStream_t stream) {
+    AggParams ap;
+    memset(&ap, 0, sizeof(ap));
+    ap.g = pl.g;
+    const Geom& g = pl.g;
+    const int chans = ROW_BYTES / dtype_size(in_dtype);
+    bool tma = tma_ok(t0, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
+               tma_ok(t1, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
+               tma_ok(t2, g.B, g.L, g.D, sb2, sl2, dtype_size(dt2)) && env_int("QSSM_NO_TMA", 0) == 0;
+    ap.g.use_tma = tma ? 1 : 0;
+    int rc;
+    if ((rc = fill_desc(ap.t0, t0, in_dtype, g.B, g.L, g.D, sb, sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(ap.t1, t1, in_dtype, g.B, g.L, g.D, sb, sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(ap.t2, t2, dt2, g.B, g.L, g.D, sb2, sl2, chans, TT, tma))) return rc;
+    ap.A = A;
+    ap.H = H;
+    const int stage = 2 * TT * ROW_BYTES + TT * chans * dtype_size(dt2);
+    ap.g.n_stages = pick_stages(pl.chains, stage, 0, 0);
+    const int smem = ap.g.n_stages * stage + MAX_STAGES * 8;
+    if (!reverse) {
+        QSSM_DISPATCH(in_dtype, in_dtype, { rc = launch(scan_agg_kernel<Tin, Tout, false>, ap, pl.chains, smem, stream); });
+    } else {
+        QSSM_DISPATCH(in_dtype, dt2, { rc = launch(scan_agg_kernel<Tin, Tout, true>, ap, pl.chains, smem, stream); });
+    }
+    return rc;
+}
+
+int resolve_segments(int n_seg_req, long long B, long long L, long long D, int in_dtype, const void* ws,
+                     size_t ws_bytes, int* n_seg_out) {
+    int n_seg = n_seg_req > 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
+    if (n_seg > 1) {
+        // make_plan may lower the count after rounding segments to whole tiles; size for the request
+        const size_t need = ws_bytes_for(B, D, n_seg);
+        if (ws == nullptr || ws_bytes < need) {
+            if (n_seg_req > 1) return QSSM_E_WS;
+            n_seg = 1;
+        }
+    }
+    *n_seg_out = n_seg;
+    return 0;
+}
+
+}  // namespace
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+int qssm_version(void) { return 100; }
+
+int qssm_tile_rows(void) { return TT; }
+
+const char* qssm_status_string(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case QSSM_E_NULL: return "a required pointer is NULL";
+        case QSSM_E_SHAPE: return "bad shape";
+        case QSSM_E_DTYPE: return "unknown dtype or unsupported in/out dtype pair";
+        case QSSM_E_STRIDE: return "bad stride";
+        case QSSM_E_NEED_H: return "backward needs tile_h or h_saved";
+        case QSSM_E_WS: return "workspace too small for the requested segment count";
+        case QSSM_E_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
+        case QSSM_S_TMA_TIMEOUT: return "device: bounded wait on a bulk-copy barrier expired";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown qssm error";
+}
+
+size_t qssm_workspace_bytes(int64_t B, int64_t L, int64_t D, int in_dtype) {
+    return ws_bytes_for(B, D, auto_segments(B, L, D, in_dtype));
+}
+
+int qssm_auto_segments(int64_t B, int64_t L, int64_t D, int in_dtype) { return auto_segments(B, L, D, in_dtype); }
+
+int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, void* y, float* h_saved,
+                  float* tile_h, const float* h_in, float* h_last, void* ws, size_t ws_bytes, int64_t B,
+                  int64_t L, int64_t D, int64_t in_stride_b, int64_t in_stride_l, int64_t out_stride_b,
+                  int64_t out_stride_l, int in_dtype, int out_dtype, int n_seg_req, int* status_word,
+                  void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int rc = check_common(B, L, D, in_dtype, out_dtype);
+    if (rc) return rc;
+    if (B == 0 || L == 0 || D == 0) {
+        if (h_last != nullptr && B > 0 && D > 0) {  // L == 0: the state passes through
+            if (h_in != nullptr)
+                return (int)cudaMemcpyAsync(h_last, h_in, (size_t)B * D * 4, cudaMemcpyDeviceToDevice, stream);
+            return (int)cudaMemsetAsync(h_last, 0, (size_t)B * D * 4, stream);
+        }
+        return 0;
+    }
+    if (x == nullptr || a == nullptr || b == nullptr || y == nullptr) return QSSM_E_NULL;
+    if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
+    if ((rc = check_strides(L, D, out_stride_b, out_stride_l))) return rc;
+
+    int n_seg = 1;
+    if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
+    Plan pl;
+    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    n_seg = pl.g.n_seg;
+
+    const float* seeds = h_in;
+    if (n_seg > 1) {
+        SegScratch sc = carve(ws, B, n_seg, D);
+        rc = run_aggregate(false, x, a, b, sc.A, sc.H, pl, in_stride_b, in_stride_l, in_stride_b, in_stride_l,
+                           in_dtype, in_dtype, stream);
+        if (rc) return rc;
+        const long long n = B * D;
+        seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(sc.A, sc.H, h_in, sc.seeds, nullptr,
+                                                                          nullptr, B, n_seg, D, 0);
+        if ((rc = (int)cudaGetLastError())) return rc;
+        seeds = sc.seeds;
+    }
+
+    FwdParams fp;
+    memset(&fp, 0, sizeof(fp));
+    fp.g = pl.g;
+    const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+    const int chans = ROW_BYTES / es;
+    const long long hs_sb = L * D, hs_sl = D;
+    bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+               tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
+               tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo) &&
+               tma_ok(h_saved, B, L, D, hs_sb, hs_sl, 4);
+    fp.g.use_tma = tma ? 1 : 0;
+    if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, chans, TT, tma))) return rc;
+    fp.tile_h = tile_h;
+    fp.h_in = seeds;
+    fp.h_last = h_last;
+
+    const int nin = c != nullptr ? 4 : 3;
+    const int stage = nin * TT * ROW_BYTES;
+    const int outbuf = TT * chans * eo + (h_saved != nullptr ? TT * chans * 4 : 0);
+    fp.g.n_stages = pick_stages(pl.chains, stage, 2 * outbuf, 0);
+    const int smem = fp.g.n_stages * stage + 2 * outbuf + MAX_STAGES * 8;
+
+#define QSSM_FWD_CASE(HAS_C, SAVE_H) \
+    QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_fwd_kernel<Tin, Tout, HAS_C, SAVE_H>, fp, pl.chains, smem, stream); })
+    if (c != nullptr && h_saved != nullptr) QSSM_FWD_CASE(true, true);
+    else if (c != nullptr) QSSM_FWD_CASE(true, false);
+    else if (h_saved != nullptr) QSSM_FWD_CASE(false, true);
+    else QSSM_FWD_CASE(false, false);
+#undef QSSM_FWD_CASE
+    return rc;
+}
+
+int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, const void* dy,
+                  const float* h_saved, const float* tile_h, const float* h_in, const float* g_in,
+                  float* g_first, void* dx, void* da, void* db, void* dc, void* ws, size_t ws_bytes, int64_t B,
+                  int64_t L, int64_t D, int64_t in_stride_b, int64_t in_stride_l, int64_t dy_stride_b,
+                  int64_t dy_stride_l, int in_dtype, int out_dtype, int n_seg_req, int* status_word,
+                  void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int rc = check_common(B, L, D, in_dtype, out_dtype);
+    if (rc) return rc;
+    if (B == 0 || L == 0 || D == 0) {
+        if (g_first != nullptr && B > 0 && D > 0) {
+            if (g_in != nullptr)
+                return (int)cudaMemcpyAsync(g_first, g_in, (size_t)B * D * 4, cudaMemcpyDeviceToDevice, stream);
+            return (int)cudaMemsetAsync(g_first, 0, (size_t)B * D * 4, stream);
+        }
+        return 0;
+    }
+    if (x == nullptr || a == nullptr || b == nullptr || c == nullptr || dy == nullptr || dx == nullptr ||
+        da == nullptr || db == nullptr || dc == nullptr)
+        return QSSM_E_NULL;
+    if (h_saved == nullptr && tile_h == nullptr) return QSSM_E_NEED_H;
+    if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
+    if ((rc = check_strides(L, D, dy_stride_b, dy_stride_l))) return rc;
+
+    int n_seg = 1;
+    if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
+    Plan pl;
+    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    n_seg = pl.g.n_seg;
+
+    const float* seeds = g_in;
+    if (n_seg > 1) {
+        SegScratch sc = carve(ws, B, n_seg, D);
+        rc = run_aggregate(true, a, c, dy, sc.A, sc.H, pl, in_stride_b, in_stride_l, dy_stride_b, dy_stride_l,
+                           in_dtype, out_dtype, stream);
+        if (rc) return rc;
+        const long long n = B * D;
+        seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(sc.A, sc.H, g_in, sc.seeds, nullptr,
+                                                                          nullptr, B, n_seg, D, 1);
+        if ((rc = (int)cudaGetLastError())) return rc;
+        seeds = sc.seeds;
+    }
+
+    BwdParams bp;
+    memset(&bp, 0, sizeof(bp));
+    bp.g = pl.g;
+    const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+    const int chans = ROW_BYTES / es;
+    const bool saved = h_saved != nullptr;
+    const long long n_tiles_b = (L + TT - 1) / TT;
+    const long long g_sb = L * D, g_sl = D;  // gradients and h_saved are contiguous
+    bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+               tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
+               tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(dy, B, L, D, dy_stride_b, dy_stride_l, eo) &&
+               tma_ok(dx, B, L, D, g_sb, g_sl, es) && tma_ok(da, B, L, D, g_sb, g_sl, es) &&
+               tma_ok(db, B, L, D, g_sb, g_sl, es) && tma_ok(dc, B, L, D, g_sb, g_sl, es) &&
+               (saved ? tma_ok(h_saved, B, L, D, g_sb, g_sl, 4) : tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4));
+    bp.g.use_tma = tma ? 1 : 0;
+    if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TT, tma))) return rc;
+    if (saved)
+        rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, chans, TT + 1, tma);
+    else
+        rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, 1, tma);
+    if (rc) return rc;
+    if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.dc, dc, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
+    bp.h_in = h_in;
+    bp.g_in = seeds;
+    bp.g_first = g_first;
+
+    const int hrow = chans * 4;
+    const int h_tile = saved ? (TT + 1) * hrow : hrow;
+    const int stage = 4 * TT * ROW_BYTES + TT * chans * eo + ((h_tile + 127) / 128) * 128;
+    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 1);
+    const int smem = bp.g.n_stages * stage + MAX_STAGES * 8;
+    if (saved) {
+        QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_bwd_kernel<Tin, Tout, true>, bp, pl.chains, smem, stream); });
+    } else {
+        QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_bwd_kernel<Tin, Tout, false>, bp, pl.chains, smem, stream); });
+    }
+    return rc;
+}
+
+static int aggregate_entry(bool reverse, const void* t0, const void* t1, const void* t2, float* A, float* H,
+                           void* ws, size_t ws_bytes, int64_t B, int64_t L, int64_t D, int64_t sb, int64_t sl,
+                           int64_t sb2, int64_t sl2, int in_dtype, int dt2, int n_seg_req, int* status_word,
+                           cudaStream_t stream) {
+    int rc = check_common(B, L, D, in_dtype, dt2);
+    if (rc) return rc;
+    if (B == 0 || D == 0) return 0;
+    if (A == nullptr || H == nullptr) return QSSM_E_NULL;
+    if (L == 0) {  // identity aggregate
+        const long long n = B * D;
+        rc = (int)cudaMemsetAsync(H, 0, (size_t)n * 4, stream);
+        if (rc) return rc;
+        // prod over an empty range is 1: fold zero aggregates with seed-less totals
+        seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(nullptr, nullptr, nullptr, nullptr, A,
+                                                                          nullptr, B, 0, D, 0);
+        return (int)cudaGetLastError();
+    }
+    if (t0 == nullptr || t1 == nullptr || t2 == nullptr) return QSSM_E_NULL;
+    if ((rc = check_strides(L, D, sb, sl))) return rc;
+    if ((rc = check_strides(L, D, sb2, sl2))) return rc;
+    int n_seg = 1;
+    if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
+    Plan pl;
+    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    n_seg = pl.g.n_seg;
+    if (n_seg == 1) return run_aggregate(reverse, t0, t1, t2, A, H, pl, sb, sl, sb2, sl2, in_dtype, dt2, stream);
+    SegScratch sc = carve(ws, B, n_seg, D);
+    rc = run_aggregate(reverse, t0, t1, t2, sc.A, sc.H, pl, sb, sl, sb2, sl2, in_dtype, dt2, stream);
+    if (rc) return rc;
+    const long long n = B * D;
+    seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(sc.A, sc.H, nullptr, nullptr, A, H, B, n_seg,
+                                                                      D, reverse ? 1 : 0);
+    return (int)cudaGetLastError();
+}
+
+int qssm_scan_aggregate_fwd(const void* x, const void* a, const void* b, float* A, float* H, void* ws,
+                            size_t ws_bytes, int64_t B, int64_t L, int64_t D, int64_t in_stride_b,
+                            int64_t in_stride_l, int in_dtype, int n_seg, int* status_word, void* stream) {
+    return aggregate_entry(false, x, a, b, A, H, ws, ws_bytes, B, L, D, in_stride_b, in_stride_l, in_stride_b,
+                           in_stride_l, in_dtype, in_dtype, n_seg, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int qssm_scan_aggregate_bwd(const void* a, const void* c, const void* dy, float* P, float* Q, void* ws,
+                            size_t ws_bytes, int64_t B, int64_t L, int64_t D, int64_t in_stride_b,
+                            int64_t in_stride_l, int64_t dy_stride_b, int64_t dy_stride_l, int in_dtype,
+                            int out_dtype, int n_seg, int* status_word, void* stream) {
+    return aggregate_entry(true, a, c, dy, P, Q, ws, ws_bytes, B, L, D, in_stride_b, in_stride_l, dy_stride_b,
+                           dy_stride_l, in_dtype, out_dtype, n_seg, status_word, static_cast<cudaStream_t>(stream));
+}
+
+int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k, int64_t n_chan, int64_t upto,
+                    int reverse, const float* seed, float* carry, void* stream) {
+    if (n_chan == 0) return 0;
+    if (carry == nullptr || (n > 0 && (A == nullptr || H == nullptr))) return QSSM_E_NULL;
+    if (n < 0 || n_chan < 0 || upto < 0 || upto > n || stride_k < n_chan) return QSSM_E_SHAPE;
+    carry_fold_kernel<<<(unsigned)((n_chan + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        A, H, n, stride_k, n_chan, upto, reverse, seed, carry);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,257 @@
+"""GPU parity tests: the CUDA scan (through the C ABI) against the CPU oracle on identical
+seeded inputs.  Shapes, distributions and tolerances follow the reference's own tests
+(test_forwards.py:23-90,108-114; test_backwards.py:26-116,120-125; test_scan_interface.py:7-31)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import scan_oracle as so
+from quick_ssm_b200 import _lib, scan_interface
+from quick_ssm_b200.scan_interface import scan
+from quick_ssm_b200.synth import make_inputs
+from tolerances import assert_close_f32, assert_close_half
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+SHAPES = [
+    (2, 512, 8),     # test_forwards.py __main__ case 1
+    (1, 4, 1),       # tiny, D = 1 (guarded path)
+    (1, 1024, 1),    # one channel, long
+    (2, 2048, 8),    # test_backwards.py __main__ case 1
+    (2, 32, 4),      # test_scan_interface.py
+    (1, 50, 2),      # L not a multiple of the tile, guarded path
+    (1, 7, 1),
+    (2, 64, 3),
+    (1, 1, 5),       # single step
+    (1, 16, 32),     # exactly one tile
+    (2, 17, 40),     # one row into the second tile; partial second column strip (fp32)
+    (3, 100, 72),    # partial strips for both element sizes
+    (2, 333, 130),
+    (4, 2048, 16),   # benchmark configuration 0
+]
+
+
+def _oracle(inp, dtype):
+    x, a, b, c, dy = (t.float().cpu() for t in (inp.x, inp.a, inp.b, inp.c, inp.dy))
+    h, y, _ = so.scan_forward(x, a, b, c, dtype=dtype)
+    dx, da, db, dc, _ = so.scan_backward(x, a, b, c, dy, dtype=dtype)
+    return dict(h=h, y=y, dx=dx, da=da, db=db, dc=dc)
+
+
+def _run_scan(inp, checkpoint=True, out_dtype=None, **kw):
+    x, a, b, c = (t.to(DEV).requires_grad_() for t in inp.tensors())
+    y = scan(x, a, b, c, checkpoint=checkpoint, out_dtype=out_dtype, **kw)
+    y.backward(inp.dy.to(DEV))
+    _lib.check_device_status(synchronize=True)
+    return dict(y=y, dx=x.grad, da=a.grad, db=b.grad, dc=c.grad)
+
+
+def _check(got, ref, dtype):
+    for k in ("y", "dx", "da", "db", "dc"):
+        if dtype == torch.float32:
+            assert_close_f32(got[k], ref[k], k)
+        else:
+            assert_close_half(got[k], ref[k], k)
+
+
+@pytest.fixture(params=[0, 3], ids=["seg_auto", "seg3"])
+def segments(request):
+    old = scan_interface.DEFAULT_SEGMENTS
+    scan_interface.DEFAULT_SEGMENTS = request.param
+    yield request.param
+    scan_interface.DEFAULT_SEGMENTS = old
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
+def test_fp32_matches_float64_loop(shape, checkpoint, segments):
+    inp = make_inputs(*shape, dtype=torch.float32, seed=11)
+    ref = _oracle(inp, np.float64)
+    got = _run_scan(inp, checkpoint=checkpoint)
+    _check(got, ref, torch.float32)
+
+
+@pytest.mark.parametrize("shape", [(2, 512, 8), (1, 50, 2), (3, 100, 72), (2, 333, 130), (2, 128, 256)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
+def test_half_matches_fp32_loop(shape, dtype, checkpoint, segments):
+    inp = make_inputs(*shape, dtype=dtype, seed=5)
+    ref = _oracle(inp, np.float32)
+    got = _run_scan(inp, checkpoint=checkpoint)
+    assert got["y"].dtype == dtype and got["dx"].dtype == dtype
+    _check(got, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_half_inputs_fp32_output(dtype, segments):
+    """layers.SSM asks for an fp32 result from 16-bit gates (layers.py:90-104)."""
+    inp = make_inputs(2, 200, 136, dtype=dtype, out_dtype=torch.float32, seed=9)
+    ref = _oracle(inp, np.float32)
+    got = _run_scan(inp, out_dtype=torch.float32)
+    assert got["y"].dtype == torch.float32 and got["da"].dtype == dtype
+    assert_close_f32(got["y"], _oracle(inp, np.float64)["y"], "y")
+    for k in ("dx", "da", "db", "dc"):
+        assert_close_half(got[k], ref[k], k)
+
+
+def test_invariant_to_block_and_tiles():
+    inp = make_inputs(3, 300, 48, dtype=torch.float32, seed=2)
+    base = _run_scan(inp)
+    other = _run_scan(inp, block_l=16, tile_b=1, tile_d=16)
+    for k in base:
+        assert torch.equal(base[k], other[k]), k
+
+
+def test_segment_counts_agree():
+    inp = make_inputs(2, 1000, 40, dtype=torch.float32, seed=4)
+    ref = _oracle(inp, np.float64)
+    old = scan_interface.DEFAULT_SEGMENTS
+    try:
+        for n in (1, 2, 5, 16, 63):
+            scan_interface.DEFAULT_SEGMENTS = n
+            _check(_run_scan(inp), ref, torch.float32)
+    finally:
+        scan_interface.DEFAULT_SEGMENTS = old
+
+
+def test_no_grad_and_partial_grads():
+    inp = make_inputs(2, 70, 24, dtype=torch.float32, seed=8).to(DEV)
+    with torch.no_grad():
+        y0 = scan(*inp.tensors())
+    x = inp.x.clone().requires_grad_()
+    y1 = scan(x, inp.a, inp.b, inp.c)
+    y1.backward(inp.dy)
+    assert torch.equal(y0, y1)
+    ref = _oracle(inp, np.float64)
+    assert_close_f32(x.grad, ref["dx"], "dx")
+
+
+def test_noncontiguous_views_and_mixed_dtypes():
+    big = make_inputs(2, 96, 192, dtype=torch.bfloat16, seed=3).to(DEV)
+    sl = slice(64, 192)  # channel shard: same row pitch, fewer channels
+    views = [t[:, :, sl] for t in big.tensors()]
+    y = scan(*views)
+    y_ref = scan(*[v.contiguous() for v in views])
+    assert torch.equal(y, y_ref)
+    # transposed storage (D not innermost) and a mixed-dtype call are made addressable by copying
+    xt = big.x.transpose(1, 2).contiguous().transpose(1, 2)
+    assert torch.equal(scan(xt, big.a, big.b, big.c), scan(big.x, big.a, big.b, big.c))
+    y_mixed = scan(big.x.float(), big.a, big.b, big.c)
+    assert y_mixed.dtype == torch.float32
+    inp32 = [t.float() for t in big.tensors()]
+    assert torch.allclose(y_mixed, scan(*inp32))
+
+
+def test_shape_and_backend_errors():
+    x = torch.zeros(2, 8, 4, device=DEV)
+    with pytest.raises(ValueError):
+        scan(x, x[:, :4], x, x)
+    with pytest.raises(ValueError):
+        scan(x, x, x, x, backend="cudnn")
+    with pytest.raises(RuntimeError):
+        scan(x.cpu(), x.cpu(), x.cpu(), x.cpu(), backend="triton")
+
+
+def test_empty_inputs():
+    for shape in [(2, 0, 4), (0, 8, 4), (2, 8, 0)]:
+        x = torch.zeros(shape, device=DEV, requires_grad=True)
+        y = scan(x, x, x, x)
+        assert y.shape == torch.Size(shape)
+        y.sum().backward()
+        assert x.grad.shape == torch.Size(shape)
+
+
+def test_known_answer_geometric_decay():
+    """Impulse response with a constant gate g: h(t) = g^t (forward_only.py:548-629, with a
+    gate that keeps the expected value well above the underflow that makes the reference's
+    own check degenerate)."""
+    from quick_ssm_b200.forward_only import block_scan_forward_3d
+    L, g = 1 << 16, 0.9999
+    x = torch.zeros(1, L, 8, device=DEV)
+    x[:, 0] = 1.0
+    a = torch.full_like(x, g)
+    b = torch.ones_like(x)
+    h = block_scan_forward_3d(x, a, b)
+    g32 = float(np.float32(g))
+    expect = g32 ** np.arange(L, dtype=np.float64)
+    got = h[0, :, 3].double().cpu().numpy()
+    assert np.abs(got / expect - 1).max() < 1e-5 * 50  # 65535 fp32 roundings of a running product
+    assert abs(got[-1] / expect[-1] - 1) < 5e-4
+
+
+def test_seeded_halves_equal_whole():
+    """Two sequence shards run one after the other reproduce the unsharded scan."""
+    inp = make_inputs(2, 256, 40, dtype=torch.float32, seed=6).to(DEV)
+    x, a, b, c = inp.tensors()
+    B, L, D = x.shape
+    whole = torch.empty_like(x)
+    h_last = torch.empty(B, D, device=DEV)
+    _lib.scan_fwd(x, a, b, c, whole, h_last=h_last)
+    half = L // 2
+    lo, hi = slice(0, half), slice(half, L)
+    y = torch.empty_like(x)
+    mid = torch.empty(B, D, device=DEV)
+    end = torch.empty(B, D, device=DEV)
+    _lib.scan_fwd(x[:, lo], a[:, lo], b[:, lo], c[:, lo], y[:, lo], h_last=mid)
+    _lib.scan_fwd(x[:, hi], a[:, hi], b[:, hi], c[:, hi], y[:, hi], h_in=mid, h_last=end)
+    torch.cuda.synchronize()
+    assert torch.allclose(y, whole, rtol=1e-6, atol=1e-6)
+    assert torch.allclose(end, h_last, rtol=1e-6, atol=1e-6)
+    # aggregates: h_end = A * h_in + H
+    A = torch.empty(B, D, device=DEV)
+    H = torch.empty(B, D, device=DEV)
+    _lib.aggregate_fwd(x[:, hi], a[:, hi], b[:, hi], A, H)
+    assert torch.allclose(A * mid + H, end, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(A, a[:, hi].double().prod(dim=1).float(), rtol=1e-5, atol=1e-30)
+    stack_a = torch.stack([torch.ones_like(A), A])
+    stack_h = torch.stack([mid, H])
+    folded = _lib.carry_fold(stack_a, stack_h, 2, reverse=False)
+    assert torch.allclose(folded, end, rtol=1e-5, atol=1e-6)
+
+    # backward: the later shard hands a(t0)*dh(t0) to the earlier one
+    dy = inp.dy
+    ref = _oracle(inp, np.float64)
+    grads = [torch.empty_like(x) for _ in range(4)]
+    g_mid = torch.empty(B, D, device=DEV)
+    th_lo = torch.empty(B, (half + 15) // 16, D, device=DEV)
+    th_hi = torch.empty(B, (L - half + 15) // 16, D, device=DEV)
+    _lib.scan_fwd(x[:, lo], a[:, lo], b[:, lo], c[:, lo], y[:, lo], tile_h=th_lo, h_last=mid)
+    _lib.scan_fwd(x[:, hi], a[:, hi], b[:, hi], c[:, hi], y[:, hi], tile_h=th_hi, h_in=mid)
+    out_hi = [torch.empty(B, L - half, D, device=DEV) for _ in range(4)]
+    out_lo = [torch.empty(B, half, D, device=DEV) for _ in range(4)]
+    _lib.scan_bwd(x[:, hi], a[:, hi], b[:, hi], c[:, hi], dy[:, hi], *out_hi, tile_h=th_hi, g_first=g_mid)
+    _lib.scan_bwd(x[:, lo], a[:, lo], b[:, lo], c[:, lo], dy[:, lo], *out_lo, tile_h=th_lo, g_in=g_mid)
+    torch.cuda.synchronize()
+    for k, lo_t, hi_t in zip(("dx", "da", "db", "dc"), out_lo, out_hi):
+        assert_close_f32(torch.cat([lo_t, hi_t], dim=1), ref[k], k)
+    P = torch.empty(B, D, device=DEV)
+    Q = torch.empty(B, D, device=DEV)
+    _lib.aggregate_bwd(a[:, hi], c[:, hi], dy[:, hi], P, Q)
+    assert torch.allclose(Q, g_mid, rtol=1e-5, atol=1e-6)
+
+
+def test_kernel_level_entry_points():
+    """block_scan_forward_3d -> (cumprod a, h); block_scan_backward_3d(a,b,c,x,h,dy)."""
+    from quick_ssm_b200.triton_backwards import block_scan_backward_3d
+    from quick_ssm_b200.triton_forwards import block_scan_forward_3d
+    for shape, seed in [((2, 512, 8), 42), ((1, 4, 1), 3), ((1, 1024, 1), 4), ((2, 2048, 8), 0)]:
+        torch.manual_seed(seed)
+        x = torch.randn(*shape)
+        a = torch.rand(*shape) * 0.1 + 0.9
+        b = torch.randn(*shape) * 0.1
+        c = torch.randn(*shape)
+        dy = torch.randn(*shape)
+        out_a, h = block_scan_forward_3d(x.to(DEV), a.to(DEV), b.to(DEV), BLOCK_L=128)
+        h_ref, _, _ = so.scan_forward(x, a, b, dtype=np.float64)
+        assert_close_f32(h, h_ref, "h")
+        assert torch.allclose(out_a.cpu().double(), torch.cumprod(a.double(), dim=1), rtol=1e-4, atol=1e-30)
+        grads = block_scan_backward_3d(a.to(DEV), b.to(DEV), c.to(DEV), x.to(DEV), h, dy.to(DEV))
+        ref = so.scan_backward(x, a, b, c, dy, dtype=np.float64)
+        for name, g, r in zip(("dx", "da", "db", "dc"), grads, ref):
+            assert g.dtype == torch.float32
+            assert_close_f32(g, r, name)
+    e = torch.empty(2, 0, 4, device=DEV)
+    assert block_scan_forward_3d(e, e, e)[1].shape == e.shape
