@@ -6,15 +6,16 @@
 // contraction), so the kernels are built around keeping many bytes in flight
 // with the bulk tensor copy engine (TMA) and touching every tensor once:
 //
-//  * one warp owns one "chain": a 128-byte-wide column strip of one batch
-//    entry (32 lanes x one 4-byte word: 32 fp32 or 64 fp16/bf16 channels) over
-//    a range of time steps, and walks it sequentially in tiles of TT rows;
+//  * one warp owns one "chain": a column strip of one batch entry (32 lanes x
+//    V channels, V = 1 or 2) over a range of time steps, and walks it
+//    sequentially in tiles of TB rows (TB = 16 or 32);
 //  * lane 0 issues cp.async.bulk.tensor loads of the next tiles of every input
 //    into a ring of shared-memory stages (completion on an mbarrier per
-//    stage); the warp scans the current tile out of shared memory with fp32
-//    state in registers, writes results back to shared memory and lane 0
-//    issues the bulk tensor store.  One CTA == one warp, so no CTA-wide
-//    barrier exists anywhere; many small CTAs per SM give the ring depth;
+//    stage); the warp scans the current tile out of shared memory, 16 rows at
+//    a time, with fp32 state in registers, writes results back to shared
+//    memory and lane 0 issues the bulk tensor store.  One CTA == one warp, so
+//    no CTA-wide barrier exists anywhere; many small CTAs per SM give the
+//    latency hiding;
 //  * the carry between tiles of a chain never leaves registers.  When B*D
 //    alone gives too few chains to fill the GPU the time axis is cut into
 //    segments: an aggregate kernel (reads only the tensors the carry depends
@@ -37,13 +38,14 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <type_traits>
+
 #include "../../include/qssm.h"
 
 namespace {
 
-constexpr int TT = QSSM_TILE_ROWS;  // rows per tile
-constexpr int ROW_BYTES = 128;      // bytes of one input row strip (32 lanes x 4 B)
-constexpr int MAX_STAGES = 12;
+constexpr int TS = QSSM_TILE_ROWS;  // rows scanned per register batch; granularity of tile_h
+constexpr int MAX_STAGES = 16;
 
 // ---------------------------------------------------------------------------------------------
 // element helpers
@@ -61,19 +63,25 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 // V consecutive channels of one lane, moved with a single shared-memory access.
 template <typename T, int V> struct alignas(sizeof(T) * V) Vec { T v[V]; };
 
-// Row r of a tile whose rows hold 32 lanes x V elements of T.
+// Row r of a tile whose rows hold 32 lanes x V elements of T.  Loads and the arithmetic on them
+// are kept apart so that all shared-memory loads of a 16-row batch can be in flight together.
 template <typename T, int V>
-__device__ __forceinline__ void tile_read(const unsigned char* tile, int r, int lane, float (&out)[V]) {
-    const Vec<T, V> w = reinterpret_cast<const Vec<T, V>*>(tile)[r * 32 + lane];
+__device__ __forceinline__ Vec<T, V> tile_raw(const unsigned char* tile, int r, int lane) {
+    return reinterpret_cast<const Vec<T, V>*>(tile)[r * 32 + lane];
+}
+template <typename T, int V>
+__device__ __forceinline__ void tile_put(unsigned char* tile, int r, int lane, const Vec<T, V>& w) {
+    reinterpret_cast<Vec<T, V>*>(tile)[r * 32 + lane] = w;
+}
+template <typename T, int V> __device__ __forceinline__ void unpack(const Vec<T, V>& w, float (&out)[V]) {
 #pragma unroll
     for (int i = 0; i < V; ++i) out[i] = to_f<T>(w.v[i]);
 }
-template <typename T, int V>
-__device__ __forceinline__ void tile_write(unsigned char* tile, int r, int lane, const float (&in)[V]) {
+template <typename T, int V> __device__ __forceinline__ Vec<T, V> pack(const float (&in)[V]) {
     Vec<T, V> w;
 #pragma unroll
     for (int i = 0; i < V; ++i) w.v[i] = from_f<T>(in[i]);
-    reinterpret_cast<Vec<T, V>*>(tile)[r * 32 + lane] = w;
+    return w;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -82,8 +90,8 @@ __device__ __forceinline__ void tile_write(unsigned char* tile, int r, int lane,
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -91,18 +99,17 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
@@ -112,8 +119,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 // Bounded wait: gives up after about two seconds.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
     const unsigned long long t0 = global_timer_ns();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -122,18 +128,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (it > (1u << 28)) return false;
     }
 }
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity);
+}
 
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
                                             int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(map)),
-                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -157,7 +167,7 @@ struct Geom {
     long long B, L, D;
     int n_dtiles;   // ceil(D / channels per warp)
     int n_seg;      // time segments
-    int seg_rows;   // rows per segment, a multiple of TT
+    int seg_rows;   // rows per segment, a multiple of the tile rows
     int n_stages;   // ring depth
     int use_tma;    // 0: guarded per-lane accesses
     int* status;    // may be NULL
@@ -165,7 +175,7 @@ struct Geom {
 
 struct FwdParams {
     TensorDesc x, a, b, c, y, hs;
-    float* tile_h;       // [B, ceil(L/TT), D] or NULL
+    float* tile_h;       // [B, ceil(L/TS), D] or NULL
     const float* h_in;   // [B, n_seg, D] or NULL
     float* h_last;       // [B, D] or NULL
     Geom g;
@@ -194,37 +204,47 @@ __device__ __forceinline__ void report(int* status, int code) {
     }
 }
 
-// Guarded fill of one tile (rows t0 .. t0+TT-1, this lane's V channels) with zero padding.
+// Guarded fill of `rows` rows starting at time t0 (this lane's V channels), zero padded.
 template <typename T, int V>
-__device__ __forceinline__ void plain_fill(unsigned char* tile, const TensorDesc& td, long long b, long long t0,
-                                           long long t_lim, long long d_lane, long long D, int lane) {
-    const T* base = reinterpret_cast<const T*>(td.ptr) + b * td.stride_b;
-#pragma unroll 4
-    for (int r = 0; r < TT; ++r) {
+__device__ __noinline__ void plain_fill(unsigned char* tile, const void* ptr, long long stride_b,
+                                        long long stride_l, long long b, long long t0, int rows, long long t_lim,
+                                        long long d_lane, long long D, int lane) {
+    const T* base = reinterpret_cast<const T*>(ptr) + b * stride_b;
+    for (int r = 0; r < rows; ++r) {
         Vec<T, V> w;
         const long long t = t0 + r;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const bool ok = (t >= 0) && (t < t_lim) && (d_lane + i < D);
-            w.v[i] = ok ? base[t * td.stride_l + d_lane + i] : from_f<T>(0.f);
+            w.v[i] = ok ? base[t * stride_l + d_lane + i] : from_f<T>(0.f);
         }
         reinterpret_cast<Vec<T, V>*>(tile)[r * 32 + lane] = w;
     }
 }
-// Guarded write-back of one tile.
 template <typename T, int V>
-__device__ __forceinline__ void plain_drain(const unsigned char* tile, const TensorDesc& td, long long b,
-                                            long long t0, long long t_lim, long long d_lane, long long D,
-                                            int lane) {
-    T* base = reinterpret_cast<T*>(td.ptr) + b * td.stride_b;
-#pragma unroll 4
-    for (int r = 0; r < TT; ++r) {
+__device__ __forceinline__ void plain_fill(unsigned char* tile, const TensorDesc& td, long long b, long long t0,
+                                           int rows, long long t_lim, long long d_lane, long long D, int lane) {
+    plain_fill<T, V>(tile, td.ptr, td.stride_b, td.stride_l, b, t0, rows, t_lim, d_lane, D, lane);
+}
+// Guarded write-back of `rows` rows.
+template <typename T, int V>
+__device__ __noinline__ void plain_drain(const unsigned char* tile, void* ptr, long long stride_b,
+                                         long long stride_l, long long b, long long t0, int rows, long long t_lim,
+                                         long long d_lane, long long D, int lane) {
+    T* base = reinterpret_cast<T*>(ptr) + b * stride_b;
+    for (int r = 0; r < rows; ++r) {
         const Vec<T, V> w = reinterpret_cast<const Vec<T, V>*>(tile)[r * 32 + lane];
         const long long t = t0 + r;
 #pragma unroll
         for (int i = 0; i < V; ++i)
-            if (t < t_lim && d_lane + i < D) base[t * td.stride_l + d_lane + i] = w.v[i];
+            if (t < t_lim && d_lane + i < D) base[t * stride_l + d_lane + i] = w.v[i];
     }
+}
+template <typename T, int V>
+__device__ __forceinline__ void plain_drain(const unsigned char* tile, const TensorDesc& td, long long b,
+                                            long long t0, int rows, long long t_lim, long long d_lane, long long D,
+                                            int lane) {
+    plain_drain<T, V>(tile, td.ptr, td.stride_b, td.stride_l, b, t0, rows, t_lim, d_lane, D, lane);
 }
 
 // Chain coordinates of this warp.
@@ -233,7 +253,7 @@ struct Chain {
     int seg, n_tiles;
     bool empty;
 };
-__device__ __forceinline__ Chain chain_of_block(const Geom& g, int chans_per_warp) {
+__device__ __forceinline__ Chain chain_of_block(const Geom& g, int chans_per_warp, int tile_rows) {
     Chain c;
     const long long id = blockIdx.x;
     const long long dt = id % g.n_dtiles;
@@ -245,33 +265,91 @@ __device__ __forceinline__ Chain chain_of_block(const Geom& g, int chans_per_war
     c.t_end = c.t_begin + g.seg_rows;
     if (c.t_end > g.L) c.t_end = g.L;
     c.empty = c.t_begin >= c.t_end;
-    c.n_tiles = c.empty ? 0 : static_cast<int>((c.t_end - c.t_begin + TT - 1) / TT);
+    c.n_tiles = c.empty ? 0 : static_cast<int>((c.t_end - c.t_begin + tile_rows - 1) / tile_rows);
     return c;
 }
+
+// Position in the ring of stages (stage index and barrier phase), advanced without divisions.
+struct RingPos {
+    int s;
+    uint32_t phase;
+    __device__ __forceinline__ void advance(int n_stages) {
+        if (++s == n_stages) {
+            s = 0;
+            phase ^= 1u;
+        }
+    }
+};
 
 // ---------------------------------------------------------------------------------------------
 // forward:  y = c*h (HAS_C) or y = h; optional fp32 h, optional tile boundary states
 // ---------------------------------------------------------------------------------------------
-template <typename Tin, typename Tout, bool HAS_C, bool SAVE_H>
+template <typename Tin, typename Tout, int V, bool HAS_C, bool SAVE_H, bool FULL>
+__device__ __forceinline__ void fwd_batch(const unsigned char* sx, const unsigned char* sa, const unsigned char* sb,
+                                          const unsigned char* sc, unsigned char* oy, unsigned char* oh, int lane,
+                                          int nrows, float (&h)[V]) {
+    Vec<Tin, V> xw[TS], aw[TS], bw[TS], cw[HAS_C ? TS : 1];
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        xw[r] = tile_raw<Tin, V>(sx, r, lane);
+        aw[r] = tile_raw<Tin, V>(sa, r, lane);
+        bw[r] = tile_raw<Tin, V>(sb, r, lane);
+        if (HAS_C) cw[r] = tile_raw<Tin, V>(sc, r, lane);
+    }
+    Vec<Tout, V> yw[TS];
+    Vec<float, V> hw[SAVE_H ? TS : 1];
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        float xv[V], av[V], bv[V], yv[V];
+        unpack<Tin, V>(xw[r], xv);
+        unpack<Tin, V>(aw[r], av);
+        unpack<Tin, V>(bw[r], bv);
+        if (FULL || r < nrows) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) h[i] = fmaf(av[i], h[i], bv[i] * xv[i]);
+        }
+        if (HAS_C) {
+            float cv[V];
+            unpack<Tin, V>(cw[r], cv);
+#pragma unroll
+            for (int i = 0; i < V; ++i) yv[i] = cv[i] * h[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) yv[i] = h[i];
+        }
+        yw[r] = pack<Tout, V>(yv);
+        if (SAVE_H) hw[r] = pack<float, V>(h);
+    }
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        tile_put<Tout, V>(oy, r, lane, yw[r]);
+        if (SAVE_H) tile_put<float, V>(oh, r, lane, hw[r]);
+    }
+}
+
+template <typename Tin, typename Tout, int V, int TB, bool HAS_C, bool SAVE_H>
 __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ FwdParams p) {
-    constexpr int V = 4 / sizeof(Tin);
     constexpr int DT = 32 * V;
+    constexpr int NSUB = TB / TS;
     constexpr int NIN = HAS_C ? 4 : 3;
-    constexpr int IN_TILE = TT * ROW_BYTES;
-    constexpr int OUT_TILE = TT * 32 * V * (int)sizeof(Tout);
-    constexpr int HS_TILE = SAVE_H ? TT * 32 * V * 4 : 0;
+    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
+    constexpr int OUT_ROW = 32 * V * (int)sizeof(Tout);
+    constexpr int H_ROW = 32 * V * 4;
+    constexpr int IN_TILE = TB * IN_ROW;
+    constexpr int OUT_TILE = TB * OUT_ROW;
+    constexpr int HS_TILE = SAVE_H ? TB * H_ROW : 0;
     constexpr int STAGE = NIN * IN_TILE;
     constexpr int OUTBUF = OUT_TILE + HS_TILE;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const Geom& g = p.g;
     const int NS = g.n_stages;
-    unsigned char* const stages = smem;
-    unsigned char* const outbuf = smem + (size_t)NS * STAGE;
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(outbuf + 2 * OUTBUF);
+    unsigned char* const outbuf = smem + NS * STAGE;
+    const uint32_t bars = smem_u32(outbuf + 2 * OUTBUF);
+    const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT);
+    const Chain ch = chain_of_block(g, DT, TB);
     if (ch.empty) return;
     const long long d_lane = ch.d0 + (long long)lane * V;
     const bool tma = g.use_tma != 0;
@@ -285,99 +363,99 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
         for (int i = 0; i < V; ++i)
             if (d_lane + i < g.D) h[i] = src[d_lane + i];
     }
+    float* th_dst = nullptr;  // tile_h row of the next 16-row batch, this lane's channels
+    if (p.tile_h != nullptr) th_dst = p.tile_h + (ch.b * ((g.L + TS - 1) / TS) + ch.t_begin / TS) * g.D + d_lane;
 
     if (tma) {
         if (lane == 0) {
-            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
             fence_barrier_init();
         }
         __syncwarp();
     }
 
     const int c0 = (int)ch.d0, c2 = (int)ch.b;
-    auto issue = [&](int j) {  // lane 0 only: loads of tile j into stage j % NS
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        const int row = (int)(ch.t_begin + (long long)j * TT);
+    RingPos pf{0, 0};  // next stage to fill
+    int pf_row = (int)ch.t_begin;
+    int pf_left = ch.n_tiles;
+    auto issue = [&]() {  // lane 0 only: loads of the next tile into stage pf.s
+        const uint32_t st = smem_base + pf.s * STAGE;
+        const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
-        mbar_expect_tx(&bars[s], STAGE);
-        tma_load_3d(st + 0 * IN_TILE, &p.x.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.a.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.b.map, &bars[s], c0, row, c2);
-        if (HAS_C) tma_load_3d(st + 3 * IN_TILE, &p.c.map, &bars[s], c0, row, c2);
+        mbar_expect_tx(bar, STAGE);
+        tma_load_3d(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2);
+        if (HAS_C) tma_load_3d(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2);
+        pf.advance(NS);
+        pf_row += TB;
+        --pf_left;
     };
 
     if (tma && lane == 0) {
-        const int pre = ch.n_tiles < NS - 1 ? ch.n_tiles : NS - 1;
-        for (int j = 0; j < pre; ++j) issue(j);
+        for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
     }
 
     bool ok = true;
-    for (int j = 0; j < ch.n_tiles; ++j) {
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        unsigned char* ob = outbuf + (size_t)(j & 1) * OUTBUF;
-        const long long t0 = ch.t_begin + (long long)j * TT;
-        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+    RingPos cur{0, 0};
+    long long t0 = ch.t_begin;
+    for (int j = 0; j < ch.n_tiles; ++j, t0 += TB) {
+        unsigned char* st = smem + cur.s * STAGE;
+        unsigned char* ob = outbuf + (j & 1) * OUTBUF;
+        const int nrows = (int)((ch.t_end - t0) < TB ? (ch.t_end - t0) : TB);
 
         if (tma) {
-            if (lane == 0 && j + NS - 1 < ch.n_tiles) issue(j + NS - 1);
-            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            if (lane == 0) {
+                if (pf_left > 0) issue();
+                tma_wait_read<1>();  // the store issued two tiles ago has finished reading `ob`
+            }
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // the store issued two tiles ago must have finished reading this output buffer
-            if (lane == 0) tma_wait_read<1>();
-            __syncwarp();
         } else {
-            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            if (HAS_C) plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-        }
-
-        if (p.tile_h != nullptr) {
-            float* dst = p.tile_h + (ch.b * ((g.L + TT - 1) / TT) + t0 / TT) * g.D;
-#pragma unroll
-            for (int i = 0; i < V; ++i)
-                if (d_lane + i < g.D) dst[d_lane + i] = h[i];
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            if (HAS_C) plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
         }
 
 #pragma unroll
-        for (int r = 0; r < TT; ++r) {
-            float xv[V], av[V], bv[V], yv[V];
-            tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
-            tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
-            tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
-            if (r < nrows) {
+        for (int sub = 0; sub < NSUB; ++sub) {
+            const int left = nrows - sub * TS;
+            if (left > 0) {
+                if (th_dst != nullptr) {
 #pragma unroll
-                for (int i = 0; i < V; ++i) h[i] = fmaf(av[i], h[i], bv[i] * xv[i]);
+                    for (int i = 0; i < V; ++i)
+                        if (d_lane + i < g.D) th_dst[i] = h[i];
+                    th_dst += g.D;
+                }
+                const unsigned char* sx = st + 0 * IN_TILE + sub * TS * IN_ROW;
+                const unsigned char* sa = st + 1 * IN_TILE + sub * TS * IN_ROW;
+                const unsigned char* sb = st + 2 * IN_TILE + sub * TS * IN_ROW;
+                const unsigned char* sc = st + 3 * IN_TILE + sub * TS * IN_ROW;
+                unsigned char* oy = ob + sub * TS * OUT_ROW;
+                unsigned char* oh = ob + OUT_TILE + sub * TS * H_ROW;
+                if (left >= TS)
+                    fwd_batch<Tin, Tout, V, HAS_C, SAVE_H, true>(sx, sa, sb, sc, oy, oh, lane, TS, h);
+                else
+                    fwd_batch<Tin, Tout, V, HAS_C, SAVE_H, false>(sx, sa, sb, sc, oy, oh, lane, left, h);
             }
-            if (HAS_C) {
-                float cv[V];
-                tile_read<Tin, V>(st + 3 * IN_TILE, r, lane, cv);
-#pragma unroll
-                for (int i = 0; i < V; ++i) yv[i] = cv[i] * h[i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < V; ++i) yv[i] = h[i];
-            }
-            tile_write<Tout, V>(ob, r, lane, yv);
-            if (SAVE_H) tile_write<float, V>(ob + OUT_TILE, r, lane, h);
         }
 
         if (tma) {
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(&p.y.map, ob, c0, (int)t0, c2);
-                if (SAVE_H) tma_store_3d(&p.hs.map, ob + OUT_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.y.map, smem_u32(ob), c0, (int)t0, c2);
+                if (SAVE_H) tma_store_3d(&p.hs.map, smem_u32(ob + OUT_TILE), c0, (int)t0, c2);
                 tma_commit();
             }
         } else {
-            plain_drain<Tout, V>(ob, p.y, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            if (SAVE_H) plain_drain<float, V>(ob + OUT_TILE, p.hs, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tout, V>(ob, p.y, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            if (SAVE_H) plain_drain<float, V>(ob + OUT_TILE, p.hs, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
         }
         __syncwarp();
+        cur.advance(NS);
     }
 
     if (tma && lane == 0) tma_wait_all();
@@ -394,34 +472,116 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward: reverse scan of dh with h rebuilt per tile (tile_h) or read (h_saved)
-// The carry between tiles is G(t) = a(t) * dh(t), so no halo row of `a` is needed.
+// backward: reverse scan of dh with h rebuilt per 16-row batch (tile_h) or read (h_saved).
+// The carry between batches is G(t) = a(t) * dh(t), so no halo row of `a` is needed.
 // Gradients overwrite the shared-memory slots of x, a, b, c and are stored from there.
 // ---------------------------------------------------------------------------------------------
-template <typename Tin, typename Tdy, bool SAVED_H>
+template <typename Tin, typename Tdy, int V, bool SAVED_H, bool FULL>
+__device__ __forceinline__ void bwd_batch(unsigned char* sx, unsigned char* sa, unsigned char* sb, unsigned char* sc,
+                                          const unsigned char* sg, const unsigned char* sh, int lane, int nrows,
+                                          bool first_rows, const float* h_in_lane, long long d_lane, long long D,
+                                          float (&G)[V]) {
+    Vec<Tin, V> xw[TS], aw[TS], bw[TS], cw[TS];
+    Vec<Tdy, V> gw[TS];
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        xw[r] = tile_raw<Tin, V>(sx, r, lane);
+        aw[r] = tile_raw<Tin, V>(sa, r, lane);
+        bw[r] = tile_raw<Tin, V>(sb, r, lane);
+    }
+    // h(t0-1 .. t0+TS-1): entry 0 is the state before the batch
+    float hreg[TS + 1][V];
+    if (SAVED_H) {
+#pragma unroll
+        for (int r = 0; r <= TS; ++r) {
+            const Vec<float, V> w = tile_raw<float, V>(sh, r, lane);
+            unpack<float, V>(w, hreg[r]);
+        }
+        if (first_rows && h_in_lane != nullptr) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) hreg[0][i] = (d_lane + i < D) ? h_in_lane[i] : 0.f;
+        }
+    } else {
+        const Vec<float, V> w = tile_raw<float, V>(sh, 0, lane);
+        unpack<float, V>(w, hreg[0]);
+    }
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        cw[r] = tile_raw<Tin, V>(sc, r, lane);
+        gw[r] = tile_raw<Tdy, V>(sg, r, lane);
+    }
+    if (!SAVED_H) {
+#pragma unroll
+        for (int r = 0; r < TS; ++r) {
+            float xv[V], av[V], bv[V];
+            unpack<Tin, V>(xw[r], xv);
+            unpack<Tin, V>(aw[r], av);
+            unpack<Tin, V>(bw[r], bv);
+#pragma unroll
+            for (int i = 0; i < V; ++i) hreg[r + 1][i] = fmaf(av[i], hreg[r][i], bv[i] * xv[i]);
+        }
+    }
+#pragma unroll
+    for (int r = TS - 1; r >= 0; --r) {
+        float xv[V], av[V], bv[V], cv[V], gy[V];
+        unpack<Tin, V>(xw[r], xv);
+        unpack<Tin, V>(aw[r], av);
+        unpack<Tin, V>(bw[r], bv);
+        unpack<Tin, V>(cw[r], cv);
+        unpack<Tdy, V>(gw[r], gy);
+        float dxv[V], dav[V], dbv[V], dcv[V];
+        const bool live = FULL || r < nrows;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float dh = fmaf(cv[i], gy[i], G[i]);
+            dxv[i] = dh * bv[i];
+            dbv[i] = dh * xv[i];
+            dav[i] = dh * hreg[r][i];
+            dcv[i] = gy[i] * hreg[r + 1][i];
+            if (live) G[i] = av[i] * dh;
+        }
+        // reuse the input words for the gradients: x -> dx, a -> da, b -> db, c -> dc
+        xw[r] = pack<Tin, V>(dxv);
+        aw[r] = pack<Tin, V>(dav);
+        bw[r] = pack<Tin, V>(dbv);
+        cw[r] = pack<Tin, V>(dcv);
+    }
+#pragma unroll
+    for (int r = 0; r < TS; ++r) {
+        tile_put<Tin, V>(sx, r, lane, xw[r]);
+        tile_put<Tin, V>(sa, r, lane, aw[r]);
+        tile_put<Tin, V>(sb, r, lane, bw[r]);
+        tile_put<Tin, V>(sc, r, lane, cw[r]);
+    }
+}
+
+template <typename Tin, typename Tdy, int V, int TB, bool SAVED_H>
 __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ BwdParams p) {
-    constexpr int V = 4 / sizeof(Tin);
     constexpr int DT = 32 * V;
-    constexpr int IN_TILE = TT * ROW_BYTES;
-    constexpr int DY_TILE = TT * 32 * V * (int)sizeof(Tdy);
-    constexpr int HROW = 32 * V * 4;                           // one fp32 row
-    constexpr int H_TILE = SAVED_H ? (TT + 1) * HROW : HROW;   // rows t0-1 .. t0+TT-1, or the boundary row
-    constexpr int STAGE = 4 * IN_TILE + DY_TILE + ((H_TILE + 127) / 128) * 128;
+    constexpr int NSUB = TB / TS;
+    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
+    constexpr int DY_ROW = 32 * V * (int)sizeof(Tdy);
+    constexpr int H_ROW = 32 * V * 4;
+    constexpr int IN_TILE = TB * IN_ROW;
+    constexpr int DY_TILE = TB * DY_ROW;
+    constexpr int H_TILE = SAVED_H ? (TB + 1) * H_ROW : NSUB * H_ROW;  // rows t0-1 .. t0+TB-1, or boundary rows
+    constexpr int H_SLOT = ((H_TILE + 127) / 128) * 128;
+    constexpr int STAGE = 4 * IN_TILE + DY_TILE + H_SLOT;
     constexpr int OFF_DY = 4 * IN_TILE;
     constexpr int OFF_H = OFF_DY + DY_TILE;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const Geom& g = p.g;
     const int NS = g.n_stages;
-    unsigned char* const stages = smem;
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + (size_t)NS * STAGE);
+    const uint32_t bars = smem_u32(smem + NS * STAGE);
+    const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT);
+    const Chain ch = chain_of_block(g, DT, TB);
     if (ch.empty) return;
     const long long d_lane = ch.d0 + (long long)lane * V;
     const bool tma = g.use_tma != 0;
-    const long long tiles_per_b = (g.L + TT - 1) / TT;
+    const long long tiles_per_b = (g.L + TS - 1) / TS;
 
     float G[V];
 #pragma unroll
@@ -432,149 +592,113 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
         for (int i = 0; i < V; ++i)
             if (d_lane + i < g.D) G[i] = src[d_lane + i];
     }
+    const float* h_in_lane = (SAVED_H && p.h_in != nullptr) ? p.h_in + ch.b * g.D + d_lane : nullptr;
 
     if (tma) {
         if (lane == 0) {
-            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
             fence_barrier_init();
         }
         __syncwarp();
     }
 
     const int c0 = (int)ch.d0, c2 = (int)ch.b;
-    // processing order j = 0 .. n_tiles-1 walks the tiles from the last to the first
-    auto tile_row = [&](int j) { return ch.t_begin + (long long)(ch.n_tiles - 1 - j) * TT; };
-    auto issue = [&](int j) {
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        const int row = (int)tile_row(j);
+    // tiles are walked from the last to the first
+    RingPos pf{0, 0};
+    int pf_row = (int)(ch.t_begin + (long long)(ch.n_tiles - 1) * TB);
+    int pf_left = ch.n_tiles;
+    auto issue = [&]() {
+        const uint32_t st = smem_base + pf.s * STAGE;
+        const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
-        mbar_expect_tx(&bars[s], 4 * IN_TILE + DY_TILE + H_TILE);
-        tma_load_3d(st + 0 * IN_TILE, &p.x.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.a.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.b.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 3 * IN_TILE, &p.c.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + OFF_DY, &p.dy.map, &bars[s], c0, row, c2);
+        mbar_expect_tx(bar, 4 * IN_TILE + DY_TILE + H_TILE);
+        tma_load_3d(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + OFF_DY, &p.dy.map, bar, c0, pf_row, c2);
         if (SAVED_H)
-            tma_load_3d(st + OFF_H, &p.hsrc.map, &bars[s], c0, row - 1, c2);  // row -1 reads zero fill
+            tma_load_3d(st + OFF_H, &p.hsrc.map, bar, c0, pf_row - 1, c2);  // row -1 reads zero fill
         else
-            tma_load_3d(st + OFF_H, &p.hsrc.map, &bars[s], c0, row / TT, c2);
+            tma_load_3d(st + OFF_H, &p.hsrc.map, bar, c0, pf_row / TS, c2);
+        pf.advance(NS);
+        pf_row -= TB;
+        --pf_left;
     };
 
     // Gradients are stored from the stage itself, so a stage can be refilled only after the store
     // issued from it has finished reading: prefetch distance is NS - 2.
-    const int PF = NS - 2;
     if (tma && lane == 0) {
-        const int pre = ch.n_tiles < PF ? ch.n_tiles : PF;
-        for (int j = 0; j < pre; ++j) issue(j);
+        for (int k = 0; k < NS - 2 && pf_left > 0; ++k) issue();
     }
 
     bool ok = true;
-    for (int j = 0; j < ch.n_tiles; ++j) {
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        const long long t0 = tile_row(j);
-        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+    RingPos cur{0, 0};
+    long long t0 = ch.t_begin + (long long)(ch.n_tiles - 1) * TB;
+    for (int j = 0; j < ch.n_tiles; ++j, t0 -= TB) {
+        unsigned char* st = smem + cur.s * STAGE;
+        const int nrows = (int)((ch.t_end - t0) < TB ? (ch.t_end - t0) : TB);
 
         if (tma) {
-            if (lane == 0 && j + PF < ch.n_tiles) {
-                tma_wait_read<1>();  // the store of tile j-2 (stage (j+PF) % NS) is done with its slots
-                issue(j + PF);
+            if (lane == 0 && pf_left > 0) {
+                tma_wait_read<1>();  // the store of the tile before the previous one is done with its stage
+                issue();
             }
-            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
         } else {
-            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tdy, V>(st + OFF_DY, p.dy, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            const float* hb = reinterpret_cast<const float*>(p.hsrc.ptr);
-            if (SAVED_H) {
-                for (int r = 0; r <= TT; ++r) {
-                    float w[V];
-                    const long long t = t0 - 1 + r;
-#pragma unroll
-                    for (int i = 0; i < V; ++i)
-                        w[i] = (t >= 0 && t < ch.t_end && d_lane + i < g.D)
-                                   ? hb[ch.b * p.hsrc.stride_b + t * p.hsrc.stride_l + d_lane + i]
-                                   : 0.f;
-                    tile_write<float, V>(st + OFF_H, r, lane, w);
-                }
-            } else {
-                float w[V];
-#pragma unroll
-                for (int i = 0; i < V; ++i)
-                    w[i] = (d_lane + i < g.D) ? hb[(ch.b * tiles_per_b + t0 / TT) * g.D + d_lane + i] : 0.f;
-                tile_write<float, V>(st + OFF_H, 0, lane, w);
-            }
-        }
-
-        // h(t0-1 .. t0+TT-1): row 0 of hreg is the state before the tile
-        float hreg[TT + 1][V];
-        if (SAVED_H) {
-#pragma unroll
-            for (int r = 0; r <= TT; ++r) tile_read<float, V>(st + OFF_H, r, lane, hreg[r]);
-            if (t0 == 0 && p.h_in != nullptr) {
-#pragma unroll
-                for (int i = 0; i < V; ++i) hreg[0][i] = (d_lane + i < g.D) ? p.h_in[ch.b * g.D + d_lane + i] : 0.f;
-            }
-        } else {
-            tile_read<float, V>(st + OFF_H, 0, lane, hreg[0]);
-#pragma unroll
-            for (int r = 0; r < TT; ++r) {
-                float xv[V], av[V], bv[V];
-                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
-                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
-                tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
-#pragma unroll
-                for (int i = 0; i < V; ++i) hreg[r + 1][i] = fmaf(av[i], hreg[r][i], bv[i] * xv[i]);
-            }
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.x, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.a, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 2 * IN_TILE, p.b, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 3 * IN_TILE, p.c, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tdy, V>(st + OFF_DY, p.dy, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            if (SAVED_H)
+                plain_fill<float, V>(st + OFF_H, p.hsrc, ch.b, t0 - 1, TB + 1, ch.t_end, d_lane, g.D, lane);
+            else  // tile_h is [B, tiles_per_b, D]
+                plain_fill<float, V>(st + OFF_H, p.hsrc.ptr, tiles_per_b * g.D, g.D, ch.b, t0 / TS, NSUB,
+                                     tiles_per_b, d_lane, g.D, lane);
         }
 
 #pragma unroll
-        for (int r = TT - 1; r >= 0; --r) {
-            float xv[V], av[V], bv[V], cv[V], gy[V];
-            tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
-            tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
-            tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
-            tile_read<Tin, V>(st + 3 * IN_TILE, r, lane, cv);
-            tile_read<Tdy, V>(st + OFF_DY, r, lane, gy);
-            float dxv[V], dav[V], dbv[V], dcv[V];
-            const bool live = r < nrows;
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float dh = fmaf(cv[i], gy[i], G[i]);
-                dxv[i] = dh * bv[i];
-                dbv[i] = dh * xv[i];
-                dav[i] = dh * hreg[r][i];
-                dcv[i] = gy[i] * hreg[r + 1][i];
-                if (live) G[i] = av[i] * dh;
+        for (int sub = NSUB - 1; sub >= 0; --sub) {
+            const int left = nrows - sub * TS;
+            if (left > 0) {
+                unsigned char* sx = st + 0 * IN_TILE + sub * TS * IN_ROW;
+                unsigned char* sa = st + 1 * IN_TILE + sub * TS * IN_ROW;
+                unsigned char* sb = st + 2 * IN_TILE + sub * TS * IN_ROW;
+                unsigned char* sc = st + 3 * IN_TILE + sub * TS * IN_ROW;
+                const unsigned char* sg = st + OFF_DY + sub * TS * DY_ROW;
+                const unsigned char* sh = st + OFF_H + (SAVED_H ? sub * TS * H_ROW : sub * H_ROW);
+                const bool first_rows = (t0 == 0 && sub == 0);
+                if (left >= TS)
+                    bwd_batch<Tin, Tdy, V, SAVED_H, true>(sx, sa, sb, sc, sg, sh, lane, TS, first_rows, h_in_lane,
+                                                          d_lane, g.D, G);
+                else
+                    bwd_batch<Tin, Tdy, V, SAVED_H, false>(sx, sa, sb, sc, sg, sh, lane, left, first_rows, h_in_lane,
+                                                           d_lane, g.D, G);
             }
-            tile_write<Tin, V>(st + 0 * IN_TILE, r, lane, dxv);
-            tile_write<Tin, V>(st + 1 * IN_TILE, r, lane, dav);
-            tile_write<Tin, V>(st + 2 * IN_TILE, r, lane, dbv);
-            tile_write<Tin, V>(st + 3 * IN_TILE, r, lane, dcv);
         }
 
         if (tma) {
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(&p.dx.map, st + 0 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.da.map, st + 1 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.db.map, st + 2 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.dc.map, st + 3 * IN_TILE, c0, (int)t0, c2);
+                const uint32_t sst = smem_base + cur.s * STAGE;
+                tma_store_3d(&p.dx.map, sst + 0 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.da.map, sst + 1 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.db.map, sst + 2 * IN_TILE, c0, (int)t0, c2);
+                tma_store_3d(&p.dc.map, sst + 3 * IN_TILE, c0, (int)t0, c2);
                 tma_commit();
             }
         } else {
-            plain_drain<Tin, V>(st + 0 * IN_TILE, p.dx, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_drain<Tin, V>(st + 1 * IN_TILE, p.da, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_drain<Tin, V>(st + 2 * IN_TILE, p.db, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_drain<Tin, V>(st + 3 * IN_TILE, p.dc, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 0 * IN_TILE, p.dx, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 1 * IN_TILE, p.da, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 2 * IN_TILE, p.db, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_drain<Tin, V>(st + 3 * IN_TILE, p.dc, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
         }
         __syncwarp();
+        cur.advance(NS);
     }
 
     if (tma && lane == 0) tma_wait_all();
@@ -594,22 +718,22 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
 // aggregates of a segment.  forward: (prod a, h_end from 0) from x, a, b
 //                           backward: (prod a, a(t0) dh(t0) from 0) from a, c, dy
 // ---------------------------------------------------------------------------------------------
-template <typename Tin, typename Tdy, bool REVERSE>
+template <typename Tin, typename Tdy, int V, int TB, bool REVERSE>
 __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ AggParams p) {
-    constexpr int V = 4 / sizeof(Tin);
     constexpr int DT = 32 * V;
-    constexpr int IN_TILE = TT * ROW_BYTES;
-    constexpr int T2_TILE = REVERSE ? TT * 32 * V * (int)sizeof(Tdy) : IN_TILE;
+    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
+    constexpr int IN_TILE = TB * IN_ROW;
+    constexpr int T2_TILE = REVERSE ? TB * 32 * V * (int)sizeof(Tdy) : IN_TILE;
     constexpr int STAGE = 2 * IN_TILE + T2_TILE;
 
     extern __shared__ __align__(128) unsigned char smem[];
     const Geom& g = p.g;
     const int NS = g.n_stages;
-    unsigned char* const stages = smem;
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + (size_t)NS * STAGE);
+    const uint32_t bars = smem_u32(smem + NS * STAGE);
+    const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT);
+    const Chain ch = chain_of_block(g, DT, TB);
     const long long d_lane = ch.d0 + (long long)lane * V;
     float* const outA = p.A + (ch.b * g.n_seg + ch.seg) * g.D;
     float* const outH = p.H + (ch.b * g.n_seg + ch.seg) * g.D;
@@ -627,55 +751,56 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
 
     if (tma) {
         if (lane == 0) {
-            for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
+            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
             fence_barrier_init();
         }
         __syncwarp();
     }
     const int c0 = (int)ch.d0, c2 = (int)ch.b;
-    auto tile_row = [&](int j) {
-        return ch.t_begin + (long long)(REVERSE ? ch.n_tiles - 1 - j : j) * TT;
-    };
-    auto issue = [&](int j) {
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        const int row = (int)tile_row(j);
+    RingPos pf{0, 0};
+    int pf_row = (int)(REVERSE ? ch.t_begin + (long long)(ch.n_tiles - 1) * TB : ch.t_begin);
+    int pf_left = ch.n_tiles;
+    auto issue = [&]() {
+        const uint32_t st = smem_base + pf.s * STAGE;
+        const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
-        mbar_expect_tx(&bars[s], STAGE);
-        tma_load_3d(st + 0 * IN_TILE, &p.t0.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.t1.map, &bars[s], c0, row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.t2.map, &bars[s], c0, row, c2);
+        mbar_expect_tx(bar, STAGE);
+        tma_load_3d(st + 0 * IN_TILE, &p.t0.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 1 * IN_TILE, &p.t1.map, bar, c0, pf_row, c2);
+        tma_load_3d(st + 2 * IN_TILE, &p.t2.map, bar, c0, pf_row, c2);
+        pf.advance(NS);
+        pf_row += REVERSE ? -TB : TB;
+        --pf_left;
     };
     if (tma && lane == 0) {
-        const int pre = ch.n_tiles < NS - 1 ? ch.n_tiles : NS - 1;
-        for (int j = 0; j < pre; ++j) issue(j);
+        for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
     }
     bool ok = true;
-    for (int j = 0; j < ch.n_tiles; ++j) {
-        const int s = j % NS;
-        unsigned char* st = stages + (size_t)s * STAGE;
-        const long long t0 = tile_row(j);
-        const int nrows = (int)((ch.t_end - t0) < TT ? (ch.t_end - t0) : TT);
+    RingPos cur{0, 0};
+    long long t0 = REVERSE ? ch.t_begin + (long long)(ch.n_tiles - 1) * TB : ch.t_begin;
+    for (int j = 0; j < ch.n_tiles; ++j, t0 += (REVERSE ? -TB : TB)) {
+        unsigned char* st = smem + cur.s * STAGE;
+        const int nrows = (int)((ch.t_end - t0) < TB ? (ch.t_end - t0) : TB);
         if (tma) {
-            if (lane == 0 && j + NS - 1 < ch.n_tiles) issue(j + NS - 1);
-            ok = mbar_wait_bounded(&bars[s], (uint32_t)((j / NS) & 1));
+            if (lane == 0 && pf_left > 0) issue();
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
         } else {
-            plain_fill<Tin, V>(st + 0 * IN_TILE, p.t0, ch.b, t0, ch.t_end, d_lane, g.D, lane);
-            plain_fill<Tin, V>(st + 1 * IN_TILE, p.t1, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 0 * IN_TILE, p.t0, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
+            plain_fill<Tin, V>(st + 1 * IN_TILE, p.t1, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
             if (REVERSE)
-                plain_fill<Tdy, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+                plain_fill<Tdy, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
             else
-                plain_fill<Tin, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, ch.t_end, d_lane, g.D, lane);
+                plain_fill<Tin, V>(st + 2 * IN_TILE, p.t2, ch.b, t0, TB, ch.t_end, d_lane, g.D, lane);
         }
         if (!REVERSE) {
 #pragma unroll
-            for (int r = 0; r < TT; ++r) {
+            for (int r = 0; r < TB; ++r) {
                 float xv[V], av[V], bv[V];
-                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, xv);
-                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, av);
-                tile_read<Tin, V>(st + 2 * IN_TILE, r, lane, bv);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 0 * IN_TILE, r, lane), xv);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 1 * IN_TILE, r, lane), av);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 2 * IN_TILE, r, lane), bv);
                 if (r < nrows) {
 #pragma unroll
                     for (int i = 0; i < V; ++i) { A[i] *= av[i]; H[i] = fmaf(av[i], H[i], bv[i] * xv[i]); }
@@ -683,11 +808,11 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
             }
         } else {
 #pragma unroll
-            for (int r = TT - 1; r >= 0; --r) {
+            for (int r = TB - 1; r >= 0; --r) {
                 float av[V], cv[V], gy[V];
-                tile_read<Tin, V>(st + 0 * IN_TILE, r, lane, av);
-                tile_read<Tin, V>(st + 1 * IN_TILE, r, lane, cv);
-                tile_read<Tdy, V>(st + 2 * IN_TILE, r, lane, gy);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 0 * IN_TILE, r, lane), av);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 1 * IN_TILE, r, lane), cv);
+                unpack<Tdy, V>(tile_raw<Tdy, V>(st + 2 * IN_TILE, r, lane), gy);
                 if (r < nrows) {
 #pragma unroll
                     for (int i = 0; i < V; ++i) { A[i] *= av[i]; H[i] = av[i] * fmaf(cv[i], gy[i], H[i]); }
@@ -695,6 +820,7 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
             }
         }
         __syncwarp();
+        cur.advance(NS);
     }
     if (!ok) {
         if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
@@ -829,7 +955,6 @@ int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long ro
     return r == CUDA_SUCCESS ? 0 : QSSM_E_STRIDE;
 }
 
-
 int sm_count() {
     static int n = []() {
         int dev = 0, v = 0;
@@ -840,18 +965,36 @@ int sm_count() {
     return n;
 }
 
-long long n_chains(long long B, long long D, int in_dtype) {
-    const int chans = ROW_BYTES / dtype_size(in_dtype);
-    return B * ((D + chans - 1) / chans);
+// Launch shape of one call: channels per lane (V), rows per tile (TB), segments, ring depth.
+struct Plan {
+    Geom g;
+    int V, TB;
+    long long chains;  // grid size
+};
+
+// Channels per lane.  Two channels per lane halve the shared-memory and copy-engine instructions
+// per element and measured faster whenever they still leave a couple of chains per SM; narrow
+// strips (V = 1) double the number of independent warps for small batch x channel counts.
+int pick_v(long long B, long long D) {
+    const int forced = env_int("QSSM_V", 0);
+    if (forced == 1 || forced == 2) return forced;
+    const long long chains_v2 = B * ((D + 63) / 64);
+    return chains_v2 >= 2ll * sm_count() ? 2 : 1;
 }
+int pick_tb() {
+    const int forced = env_int("QSSM_TB", 0);
+    return forced == 16 || forced == 32 ? forced : 16;
+}
+
+long long n_chains(long long B, long long D, int V) { return B * ((D + 32 * V - 1) / (32 * V)); }
 
 // Segment count: split time only when batch x channels gives fewer chains than SMs.
 int auto_segments(long long B, long long L, long long D, int in_dtype) {
     if (B <= 0 || L <= 0 || D <= 0 || dtype_size(in_dtype) == 0) return 1;
-    const long long chains = n_chains(B, D, in_dtype);
+    const long long chains = n_chains(B, D, 1);
     if (chains >= 128) return 1;
     long long want = (512 + chains - 1) / chains;
-    const long long max_by_len = L / (8 * TT);  // at least 8 tiles per segment
+    const long long max_by_len = L / (8 * 32);  // at least 256 rows per segment
     if (want > max_by_len) want = max_by_len;
     if (want < 1) want = 1;
     if (want > 4096) want = 4096;
@@ -864,35 +1007,32 @@ size_t ws_bytes_for(long long B, long long D, int n_seg) {
 }
 
 // Ring depth: spread the shared memory of an SM over the chains expected to be resident on it.
-int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int prefetch_slack) {
-    int forced = env_int("QSSM_STAGES", 0);
+int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int min_stages, int dflt_stages) {
+    const int forced = env_int("QSSM_STAGES", 0);
     long long per_sm = (chains_total + sm_count() - 1) / sm_count();
-    int max_res = env_int("QSSM_RESIDENT", 6);
+    const int max_res = env_int("QSSM_RESIDENT", 16);
     if (per_sm > max_res) per_sm = max_res;
     if (per_sm < 1) per_sm = 1;
     const int budget = (int)((227 * 1024) / per_sm) - 1024 - fixed_bytes - MAX_STAGES * 8 - 128;
     int ns = budget / stage_bytes;
+    if (ns > dflt_stages) ns = dflt_stages;
     if (forced > 0) ns = forced;
-    const int lo = 2 + prefetch_slack;
-    if (ns < lo) ns = lo;
+    if (ns < min_stages) ns = min_stages;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
-    while (ns > lo && ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 128 > 227 * 1024) --ns;
+    while (ns > min_stages && ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 128 > 227 * 1024) --ns;
     return ns;
 }
 
-struct Plan {
-    Geom g;
-    long long chains;  // grid size
-};
-
-int make_plan(Plan& pl, long long B, long long L, long long D, int in_dtype, int n_seg, int* status) {
-    const int chans = ROW_BYTES / dtype_size(in_dtype);
+int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* status) {
+    pl.V = pick_v(B, D);
+    pl.TB = pick_tb();
+    const int chans = 32 * pl.V;
     Geom& g = pl.g;
     g.B = B; g.L = L; g.D = D;
     g.n_dtiles = (int)((D + chans - 1) / chans);
     if (n_seg < 1) n_seg = 1;
     long long seg_rows = (L + n_seg - 1) / n_seg;
-    seg_rows = ((seg_rows + TT - 1) / TT) * TT;
+    seg_rows = ((seg_rows + 31) / 32) * 32;  // whole tiles for either tile height
     n_seg = (int)((L + seg_rows - 1) / seg_rows);
     g.n_seg = n_seg;
     g.seg_rows = (int)seg_rows;
@@ -917,7 +1057,7 @@ int check_common(long long B, long long L, long long D, int in_dtype, int out_dt
     if (B < 0 || L < 0 || D < 0) return QSSM_E_SHAPE;
     if (dtype_size(in_dtype) == 0 || dtype_size(out_dtype) == 0) return QSSM_E_DTYPE;
     if (!(out_dtype == in_dtype || out_dtype == QSSM_F32)) return QSSM_E_DTYPE;
-    if (L >= (1ll << 31) || B >= (1ll << 31)) return QSSM_E_SHAPE;
+    if (L >= (1ll << 31) - 64 || B >= (1ll << 31)) return QSSM_E_SHAPE;
     return 0;
 }
 int check_strides(long long L, long long D, long long sb, long long sl) {
@@ -927,15 +1067,22 @@ int check_strides(long long L, long long D, long long sb, long long sl) {
     return 0;
 }
 
-// dispatch on (in dtype, out dtype): out is the in dtype or fp32
-#define QSSM_DISPATCH(in_dt, out_dt, BODY)                                                     \
-    do {                                                                                       \
-        if ((in_dt) == QSSM_F32) { using Tin = float; using Tout = float; BODY; }              \
-        else if ((in_dt) == QSSM_F16 && (out_dt) == QSSM_F16) { using Tin = __half; using Tout = __half; BODY; } \
-        else if ((in_dt) == QSSM_F16) { using Tin = __half; using Tout = float; BODY; }        \
-        else if ((in_dt) == QSSM_BF16 && (out_dt) == QSSM_BF16) { using Tin = __nv_bfloat16; using Tout = __nv_bfloat16; BODY; } \
-        else { using Tin = __nv_bfloat16; using Tout = float; BODY; }                          \
-    } while (0)
+template <int N> using Int = std::integral_constant<int, N>;
+
+// Calls f(Tin{}, Tout{}, Int<V>{}, Int<TB>{}) for the run-time (dtype pair, V, TB).
+template <typename F> int dispatch(int in_dt, int out_dt, int V, int TB, F&& f) {
+    auto with_types = [&](auto tin, auto tout) -> int {
+        if (V == 1 && TB == 16) return f(tin, tout, Int<1>{}, Int<16>{});
+        if (V == 1) return f(tin, tout, Int<1>{}, Int<32>{});
+        if (TB == 16) return f(tin, tout, Int<2>{}, Int<16>{});
+        return f(tin, tout, Int<2>{}, Int<32>{});
+    };
+    if (in_dt == QSSM_F32) return with_types(float{}, float{});
+    if (in_dt == QSSM_F16 && out_dt == QSSM_F16) return with_types(__half{}, __half{});
+    if (in_dt == QSSM_F16) return with_types(__half{}, float{});
+    if (in_dt == QSSM_BF16 && out_dt == QSSM_BF16) return with_types(__nv_bfloat16{}, __nv_bfloat16{});
+    return with_types(__nv_bfloat16{}, float{});
+}
 
 // segment aggregates -> seeds.  A/H/seeds live in ws: three [B, n_seg, D] fp32 arrays.
 struct SegScratch {
@@ -957,26 +1104,28 @@ int run_aggregate(bool reverse, const void* t0, const void* t1, const void* t2, 
     memset(&ap, 0, sizeof(ap));
     ap.g = pl.g;
     const Geom& g = pl.g;
-    const int chans = ROW_BYTES / dtype_size(in_dtype);
+    const int chans = 32 * pl.V, TB = pl.TB;
     bool tma = tma_ok(t0, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
                tma_ok(t1, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
                tma_ok(t2, g.B, g.L, g.D, sb2, sl2, dtype_size(dt2)) && env_int("QSSM_NO_TMA", 0) == 0;
     ap.g.use_tma = tma ? 1 : 0;
     int rc;
-    if ((rc = fill_desc(ap.t0, t0, in_dtype, g.B, g.L, g.D, sb, sl, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(ap.t1, t1, in_dtype, g.B, g.L, g.D, sb, sl, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(ap.t2, t2, dt2, g.B, g.L, g.D, sb2, sl2, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(ap.t0, t0, in_dtype, g.B, g.L, g.D, sb, sl, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(ap.t1, t1, in_dtype, g.B, g.L, g.D, sb, sl, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(ap.t2, t2, dt2, g.B, g.L, g.D, sb2, sl2, chans, TB, tma))) return rc;
     ap.A = A;
     ap.H = H;
-    const int stage = 2 * TT * ROW_BYTES + TT * chans * dtype_size(dt2);
-    ap.g.n_stages = pick_stages(pl.chains, stage, 0, 0);
+    const int stage = TB * chans * (2 * dtype_size(in_dtype) + dtype_size(dt2));
+    ap.g.n_stages = pick_stages(pl.chains, stage, 0, 2, 4);
     const int smem = ap.g.n_stages * stage + MAX_STAGES * 8;
-    if (!reverse) {
-        QSSM_DISPATCH(in_dtype, in_dtype, { rc = launch(scan_agg_kernel<Tin, Tout, false>, ap, pl.chains, smem, stream); });
-    } else {
-        QSSM_DISPATCH(in_dtype, dt2, { rc = launch(scan_agg_kernel<Tin, Tout, true>, ap, pl.chains, smem, stream); });
-    }
-    return rc;
+    const int out_dt = reverse ? dt2 : in_dtype;
+    return dispatch(in_dtype, out_dt, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
+        using Tin = decltype(tin);
+        using Tout = decltype(tout);
+        constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
+        if (reverse) return launch(scan_agg_kernel<Tin, Tout, V, TBc, true>, ap, pl.chains, smem, stream);
+        return launch(scan_agg_kernel<Tin, Tin, V, TBc, false>, ap, pl.chains, smem, stream);
+    });
 }
 
 int resolve_segments(int n_seg_req, long long B, long long L, long long D, int in_dtype, const void* ws,
@@ -1003,7 +1152,7 @@ extern "C" {
 
 int qssm_version(void) { return 100; }
 
-int qssm_tile_rows(void) { return TT; }
+int qssm_tile_rows(void) { return TS; }
 
 const char* qssm_status_string(int code) {
     switch (code) {
@@ -1051,7 +1200,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    if ((rc = make_plan(pl, B, L, D, n_seg, status_word))) return rc;
     n_seg = pl.g.n_seg;
 
     const float* seeds = h_in;
@@ -1071,37 +1220,39 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     memset(&fp, 0, sizeof(fp));
     fp.g = pl.g;
     const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
-    const int chans = ROW_BYTES / es;
+    const int chans = 32 * pl.V, TB = pl.TB;
     const long long hs_sb = L * D, hs_sl = D;
     bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo) &&
                tma_ok(h_saved, B, L, D, hs_sb, hs_sl, 4);
     fp.g.use_tma = tma ? 1 : 0;
-    if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, chans, TB, tma))) return rc;
     fp.tile_h = tile_h;
     fp.h_in = seeds;
     fp.h_last = h_last;
 
     const int nin = c != nullptr ? 4 : 3;
-    const int stage = nin * TT * ROW_BYTES;
-    const int outbuf = TT * chans * eo + (h_saved != nullptr ? TT * chans * 4 : 0);
-    fp.g.n_stages = pick_stages(pl.chains, stage, 2 * outbuf, 0);
+    const int stage = nin * TB * chans * es;
+    const int outbuf = TB * chans * eo + (h_saved != nullptr ? TB * chans * 4 : 0);
+    fp.g.n_stages = pick_stages(pl.chains, stage, 2 * outbuf, 2, 4);
     const int smem = fp.g.n_stages * stage + 2 * outbuf + MAX_STAGES * 8;
+    const bool has_c = c != nullptr, save_h = h_saved != nullptr;
 
-#define QSSM_FWD_CASE(HAS_C, SAVE_H) \
-    QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_fwd_kernel<Tin, Tout, HAS_C, SAVE_H>, fp, pl.chains, smem, stream); })
-    if (c != nullptr && h_saved != nullptr) QSSM_FWD_CASE(true, true);
-    else if (c != nullptr) QSSM_FWD_CASE(true, false);
-    else if (h_saved != nullptr) QSSM_FWD_CASE(false, true);
-    else QSSM_FWD_CASE(false, false);
-#undef QSSM_FWD_CASE
-    return rc;
+    return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
+        using Tin = decltype(tin);
+        using Tout = decltype(tout);
+        constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
+        if (has_c && save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, true>, fp, pl.chains, smem, stream);
+        if (has_c) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, false>, fp, pl.chains, smem, stream);
+        if (save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, true>, fp, pl.chains, smem, stream);
+        return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, false>, fp, pl.chains, smem, stream);
+    });
 }
 
 int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, const void* dy,
@@ -1131,7 +1282,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    if ((rc = make_plan(pl, B, L, D, n_seg, status_word))) return rc;
     n_seg = pl.g.n_seg;
 
     const float* seeds = g_in;
@@ -1151,9 +1302,9 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     memset(&bp, 0, sizeof(bp));
     bp.g = pl.g;
     const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
-    const int chans = ROW_BYTES / es;
+    const int chans = 32 * pl.V, TB = pl.TB;
     const bool saved = h_saved != nullptr;
-    const long long n_tiles_b = (L + TT - 1) / TT;
+    const long long n_tiles_b = (L + TS - 1) / TS;
     const long long g_sb = L * D, g_sl = D;  // gradients and h_saved are contiguous
     bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
@@ -1162,35 +1313,36 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
                tma_ok(db, B, L, D, g_sb, g_sl, es) && tma_ok(dc, B, L, D, g_sb, g_sl, es) &&
                (saved ? tma_ok(h_saved, B, L, D, g_sb, g_sl, 4) : tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4));
     bp.g.use_tma = tma ? 1 : 0;
-    if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TB, tma))) return rc;
     if (saved)
-        rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, chans, TT + 1, tma);
+        rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, chans, TB + 1, tma);
     else
-        rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, 1, tma);
+        rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, TB / TS, tma);
     if (rc) return rc;
-    if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
-    if ((rc = fill_desc(bp.dc, dc, in_dtype, B, L, D, g_sb, g_sl, chans, TT, tma))) return rc;
+    if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, chans, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.dc, dc, in_dtype, B, L, D, g_sb, g_sl, chans, TB, tma))) return rc;
     bp.h_in = h_in;
     bp.g_in = seeds;
     bp.g_first = g_first;
 
     const int hrow = chans * 4;
-    const int h_tile = saved ? (TT + 1) * hrow : hrow;
-    const int stage = 4 * TT * ROW_BYTES + TT * chans * eo + ((h_tile + 127) / 128) * 128;
-    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 1);
+    const int h_tile = saved ? (TB + 1) * hrow : (TB / TS) * hrow;
+    const int stage = 4 * TB * chans * es + TB * chans * eo + ((h_tile + 127) / 128) * 128;
+    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 3, 3);
     const int smem = bp.g.n_stages * stage + MAX_STAGES * 8;
-    if (saved) {
-        QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_bwd_kernel<Tin, Tout, true>, bp, pl.chains, smem, stream); });
-    } else {
-        QSSM_DISPATCH(in_dtype, out_dtype, { rc = launch(scan_bwd_kernel<Tin, Tout, false>, bp, pl.chains, smem, stream); });
-    }
-    return rc;
+    return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
+        using Tin = decltype(tin);
+        using Tout = decltype(tout);
+        constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
+        if (saved) return launch(scan_bwd_kernel<Tin, Tout, V, TBc, true>, bp, pl.chains, smem, stream);
+        return launch(scan_bwd_kernel<Tin, Tout, V, TBc, false>, bp, pl.chains, smem, stream);
+    });
 }
 
 static int aggregate_entry(bool reverse, const void* t0, const void* t1, const void* t2, float* A, float* H,
@@ -1201,11 +1353,10 @@ static int aggregate_entry(bool reverse, const void* t0, const void* t1, const v
     if (rc) return rc;
     if (B == 0 || D == 0) return 0;
     if (A == nullptr || H == nullptr) return QSSM_E_NULL;
-    if (L == 0) {  // identity aggregate
+    if (L == 0) {  // identity aggregate: prod over an empty range is 1, state 0
         const long long n = B * D;
         rc = (int)cudaMemsetAsync(H, 0, (size_t)n * 4, stream);
         if (rc) return rc;
-        // prod over an empty range is 1: fold zero aggregates with seed-less totals
         seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(nullptr, nullptr, nullptr, nullptr, A,
                                                                           nullptr, B, 0, D, 0);
         return (int)cudaGetLastError();
@@ -1216,7 +1367,7 @@ static int aggregate_entry(bool reverse, const void* t0, const void* t1, const v
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, in_dtype, n_seg, status_word))) return rc;
+    if ((rc = make_plan(pl, B, L, D, n_seg, status_word))) return rc;
     n_seg = pl.g.n_seg;
     if (n_seg == 1) return run_aggregate(reverse, t0, t1, t2, A, H, pl, sb, sl, sb2, sl2, in_dtype, dt2, stream);
     SegScratch sc = carve(ws, B, n_seg, D);
