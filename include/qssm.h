@@ -47,6 +47,7 @@ extern "C" {
 #define QSSM_E_NEED_H (-5)    /* backward needs tile_h or h_saved */
 #define QSSM_E_WS (-6)        /* workspace too small for the requested segment count */
 #define QSSM_E_DRIVER (-7)    /* the CUDA driver entry point for tensor maps is unavailable */
+#define QSSM_E_STATIC_WS (-8) /* qssm_scan_fwd_static_ws: scratch needed exceeds QSSM_STATIC_WS_BYTES */
 
 /* device-side status codes written to *status_word */
 #define QSSM_S_OK 0
@@ -104,6 +105,41 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
                   int64_t out_stride_b, int64_t out_stride_l,
                   int in_dtype, int out_dtype, int n_seg,
                   int* status_word, void* stream);
+
+/*
+ * Forward scan that brings its own scratch.  No counterpart in the reference.
+ *
+ * Same arguments, results and return codes as qssm_scan_fwd, minus `ws`/`ws_bytes`.  It is meant
+ * for callers that must not, or cannot, allocate device memory around the call: a plugin inside
+ * a host runtime whose memory pool has already reserved the device heap and hands out no
+ * allocator (a raw cudaMalloc there fails or fragments the pool), a service with a "no
+ * allocation after start-up" rule, a latency-critical loop where the implicit device-wide
+ * synchronisation of cudaMalloc/cudaFree is not acceptable.  The segment aggregates and seeds that
+ * qssm_scan_fwd keeps in `ws` live instead in a fixed array of QSSM_STATIC_WS_BYTES inside the
+ * library's device image (each GPU that loads the library carries those bytes until the process
+ * ends).  The call performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ *
+ * Limits and rules
+ *   - the scratch the shape needs, 3 * B * n_seg * D * 4 bytes with n_seg = the `n_seg` argument or,
+ *     for 0, qssm_auto_segments(), must fit: otherwise QSSM_E_STATIC_WS is returned and nothing
+ *     is launched (the call never silently runs unsegmented);
+ *   - the first call on each device looks up the device address of the array (a short host-side
+ *     runtime query, done with that device current); make that first call outside any stream
+ *     capture;
+ *   - all calls on one GPU share the one array and it keeps whatever the previous call left in
+ *     it.  Nothing in it has to start at zero: every entry is written by the aggregate and carry
+ *     kernels of a call before the scan kernel of the same call reads it.  Two calls whose
+ *     kernels can overlap on the GPU (different streams, no ordering between them) race on it:
+ *     order them, or use qssm_scan_fwd with separate `ws` buffers.
+ */
+#define QSSM_STATIC_WS_BYTES (4 * 1024 * 1024)
+int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const void* c, void* y,
+                            float* h_saved, float* tile_h, const float* h_in, float* h_last,
+                            int64_t B, int64_t L, int64_t D,
+                            int64_t in_stride_b, int64_t in_stride_l,
+                            int64_t out_stride_b, int64_t out_stride_l,
+                            int in_dtype, int out_dtype, int n_seg,
+                            int* status_word, void* stream);
 
 /*
  * Backward scan for upstream gradient dy (dtype out_dtype, strides dy_stride_*):

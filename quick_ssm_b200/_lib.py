@@ -31,6 +31,8 @@ SIGNATURES = {
     "qssm_auto_segments": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int]),
     "qssm_scan_fwd": (_c_int, [_c_vp] * 5 + [_c_vp] * 4 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
                       + [_c_int] * 3 + [_c_vp, _c_vp]),
+    "qssm_scan_fwd_static_ws": (_c_int, [_c_vp] * 5 + [_c_vp] * 4 + [_c_i64] * 3 + [_c_i64] * 4 + [_c_int] * 3
+                                + [_c_vp, _c_vp]),
     "qssm_scan_bwd": (_c_int, [_c_vp] * 5 + [_c_vp] * 5 + [_c_vp] * 4 + [_c_vp, _c_sz] + [_c_i64] * 3
                       + [_c_i64] * 4 + [_c_int] * 3 + [_c_vp, _c_vp]),
     "qssm_scan_aggregate_fwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 2
@@ -178,6 +180,26 @@ def scan_fwd(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None
                                   B, L, D, sb, sl, ob, ol, code_in, code_out, int(n_seg),
                                   _status_word(dev).data_ptr(), _stream(dev))
     _rc(rc, "qssm_scan_fwd")
+
+
+def scan_fwd_static_ws(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None, n_seg: int = 0) -> None:
+    """Forward scan whose segment scratch is the library's built-in device array: this wrapper and
+    the C entry point allocate no device memory (for callers that cannot allocate around the call,
+    e.g. inside a runtime whose pool owns the device heap, or under a no-allocation-after-start-up
+    rule).  Raises when the
+    shape needs more scratch than the built-in array holds.  Calls that may overlap on one GPU
+    must be ordered by the caller, since they share that array."""
+    dev = _require_cuda(x, a, b, c, y, h_saved, tile_h, h_in, h_last)
+    B, L, D = x.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        sb, sl = _blds(x)
+        ob, ol = _blds(y)
+        rc = load().qssm_scan_fwd_static_ws(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(y), _ptr(h_saved),
+                                            _ptr(tile_h), _ptr(h_in), _ptr(h_last), B, L, D, sb, sl, ob, ol,
+                                            dtype_code(x.dtype), dtype_code(y.dtype), int(n_seg),
+                                            _status_word(dev).data_ptr(), _stream(dev))
+    _rc(rc, "qssm_scan_fwd_static_ws")
 
 
 def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=None, g_in=None, g_first=None,

@@ -1143,6 +1143,34 @@ int resolve_segments(int n_seg_req, long long B, long long L, long long D, int i
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for qssm_scan_fwd_static_ws: lives in the library's device image, so every
+// GPU that loads the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_ws[QSSM_STATIC_WS_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+void* g_static_ws_addr[MAX_DEVICES];  // device address of g_static_ws on each device, once resolved
+
+// Device address of the built-in scratch on the current device.  `g_static_ws` in host code is only
+// a handle for the runtime, never a pointer a kernel could use, so the address is asked for once
+// per device (with that device current) and cached.
+int static_ws_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return QSSM_E_SHAPE;
+    void* p = __atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        e = cudaGetSymbolAddress(&p, g_static_ws);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return QSSM_E_NULL;
+        __atomic_store_n(&g_static_ws_addr[dev], p, __ATOMIC_RELEASE);  // same value from every thread
+    }
+    *out = p;
+    return 0;
+}
+
 }  // namespace
 
 // =============================================================================================
@@ -1164,6 +1192,8 @@ const char* qssm_status_string(int code) {
         case QSSM_E_NEED_H: return "backward needs tile_h or h_saved";
         case QSSM_E_WS: return "workspace too small for the requested segment count";
         case QSSM_E_DRIVER: return "CUDA driver entry point cuTensorMapEncodeTiled unavailable";
+        case QSSM_E_STATIC_WS:
+            return "segment scratch for this shape exceeds QSSM_STATIC_WS_BYTES, the built-in maximum";
         case QSSM_S_TMA_TIMEOUT: return "device: bounded wait on a bulk-copy barrier expired";
         default: break;
     }
@@ -1253,6 +1283,23 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
         if (save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, true>, fp, pl.chains, smem, stream);
         return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, false>, fp, pl.chains, smem, stream);
     });
+}
+
+int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const void* c, void* y, float* h_saved,
+                            float* tile_h, const float* h_in, float* h_last, int64_t B, int64_t L, int64_t D,
+                            int64_t in_stride_b, int64_t in_stride_l, int64_t out_stride_b, int64_t out_stride_l,
+                            int in_dtype, int out_dtype, int n_seg_req, int* status_word, void* stream) {
+    int rc = check_common(B, L, D, in_dtype, out_dtype);
+    if (rc) return rc;
+    // Scratch the segmented scan would need; refuse rather than quietly run unsegmented.
+    const int n_seg = n_seg_req > 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
+    const size_t need = ws_bytes_for(B, D, n_seg);
+    if (need > (size_t)QSSM_STATIC_WS_BYTES) return QSSM_E_STATIC_WS;
+    void* ws = nullptr;
+    if ((rc = static_ws_address(&ws))) return rc;
+    return qssm_scan_fwd(x, a, b, c, y, h_saved, tile_h, h_in, h_last, ws, (size_t)QSSM_STATIC_WS_BYTES, B, L, D,
+                         in_stride_b, in_stride_l, out_stride_b, out_stride_l, in_dtype, out_dtype, n_seg_req,
+                         status_word, stream);
 }
 
 int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, const void* dy,
