@@ -1,0 +1,105 @@
+"""Callers of the scan on the GPU: the SSM layer stack (16-bit gates, fp32 scan output) and the
+sequence-sharded scan over NCCL when the box has more than one GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import scan_oracle as so
+from quick_ssm_b200 import SSM, _lib
+from quick_ssm_b200.synth import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("compute_dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_ssm_layer_gpu_matches_torch_backend(compute_dtype):
+    torch.manual_seed(0)
+    layer = SSM(hidden_size=64, state_size_mult=4.0, compute_dtype=compute_dtype, device="cuda")
+    x = torch.randn(2, 200, 64, device="cuda")
+    outs = {}
+    for backend in ("auto", "torch"):
+        xi = x.clone().requires_grad_()
+        layer.zero_grad()
+        y = layer(xi, block_l=128, checkpoint=True, tile_b=1, tile_d=512, scan_out_dtype=torch.float32,
+                  backend=backend)
+        y.pow(2).mean().backward()
+        outs[backend] = (y.detach(), xi.grad, layer.A_proj.weight.grad.clone())
+    tol = dict(rtol=1e-3, atol=1e-4) if compute_dtype == torch.float32 else dict(rtol=3e-2, atol=3e-3)
+    for got, ref, name in zip(outs["auto"], outs["torch"], ("y", "dx", "dW_A")):
+        assert torch.allclose(got, ref, **tol), name
+    _lib.check_device_status(synchronize=True)
+
+
+def test_copy_model_trains_a_few_steps():
+    """The shape of the reference's copy task (copy_train.py:20-38): embed -> SSM -> head."""
+    torch.manual_seed(0)
+    vocab, hidden = 62, 64
+    embed = torch.nn.Embedding(vocab, hidden, device="cuda")
+    ssm = SSM(hidden_size=hidden, state_size_mult=4.0, compute_dtype=torch.bfloat16, device="cuda")
+    head = torch.nn.Linear(hidden, vocab, device="cuda")
+    params = list(embed.parameters()) + list(ssm.parameters()) + list(head.parameters())
+    opt = torch.optim.AdamW(params, lr=3e-3)
+    losses = []
+    for _ in range(30):
+        src = torch.randint(0, vocab, (16, 8), device="cuda")
+        inp = torch.cat([src, torch.cat([torch.zeros_like(src[:, :1]), src[:, :-1]], 1)], 1)
+        labels = torch.cat([torch.full_like(src, -100), src], 1)
+        logits = head(ssm(embed(inp), block_l=128, checkpoint=True, tile_b=1, tile_d=512,
+                          scan_out_dtype=torch.float32))
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, vocab), labels.reshape(-1), ignore_index=-100)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert np.isfinite(losses).all() and losses[-1] < losses[0]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_worker(rank, world, port, out_dir, dtype):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from quick_ssm_b200.sharded import scan_sequence_sharded
+        L = 4096
+        inp = make_inputs(2, L, 96, dtype=dtype, seed=3, decay="near_unit")
+        per = L // world
+        sl = slice(rank * per, (rank + 1) * per)
+        x, a, b, c = (t[:, sl].cuda().requires_grad_() for t in inp.tensors())
+        y = scan_sequence_sharded(x, a, b, c)
+        y.backward(inp.dy[:, sl].cuda())
+        torch.cuda.synchronize()
+        torch.save({k: v.detach().float().cpu() for k, v in
+                    dict(y=y, dx=x.grad, da=a.grad, db=b.grad, dc=c.grad).items()},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["fp32", "fp16"])
+def test_sequence_sharded_scan_over_nccl(tmp_path, dtype):
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path), dtype), nprocs=world, join=True)
+    parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
+    inp = make_inputs(2, 4096, 96, dtype=dtype, seed=3, decay="near_unit")
+    acc = np.float64 if dtype == torch.float32 else np.float32
+    f = [t.float() for t in (inp.x, inp.a, inp.b, inp.c, inp.dy)]
+    _, y_ref, _ = so.scan_forward(*f[:4], dtype=acc)
+    g_ref = so.scan_backward(*f, dtype=acc)
+    got = {k: torch.cat([p[k] for p in parts], dim=1).numpy() for k in parts[0]}
+    from tolerances import assert_close_f32, assert_close_half
+    check = assert_close_f32 if dtype == torch.float32 else assert_close_half
+    check(got["y"], y_ref, "y")
+    for k, ref in zip(("dx", "da", "db", "dc"), g_ref):
+        check(got[k], ref, k)
