@@ -34,9 +34,10 @@ UNIT = "Gelem/s"
 CFG = dict(B=8, L=8192, D=4096)
 WORKLOAD = "cfg1: scan fwd+bwd, B=8 L=8192 D=4096, bf16 storage / fp32 accumulate, checkpoint=True"
 
-# DRAM bytes (read + write) of one backward launch on this workload, from an ncu capture of the
-# same kernel on a quarter of the batch (B=2), scaled by 4: traffic grows in proportion to B.
-NCU_BWD_TRAFFIC_BYTES_B2 = 687.97e6 + 494.12e6
+# DRAM bytes (read + write) of one backward launch, from an ncu capture of the same kernel on a
+# quarter of the sequence (`--seq-len 2048`: same chains, same residency, 1.3 GB resident);
+# traffic grows in proportion to L, so a full launch is this times L/2048.
+NCU_BWD_TRAFFIC_BYTES_L2048 = 687.97e6 + 494.12e6
 
 
 def _peak_hbm():
@@ -190,7 +191,7 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    B, L, D = CFG["B"], CFG["L"], CFG["D"]
+    B, L, D = CFG["B"], args.seq_len or CFG["L"], CFG["D"]
     dtype = torch.bfloat16
     n_elem = B * L * D
     es = 2
@@ -234,6 +235,13 @@ def run_gpu(args):
     total_ms = t_begin.elapsed_time(t_end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+
+    if args.no_e2e:
+        if rank == 0:
+            print(json.dumps({"note": "profiling run, not a bench line", "L": L, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through host buffers (pinned host memory in and out, every step) ----
     e2e_steps = max(2, min(K, 5))
@@ -281,7 +289,7 @@ def run_gpu(args):
                        "l2": "no flush needed: each step streams 7.5 GB of distinct tensors, far above the 126 MB L2"},
             "roofline": {"bound": "hbm", "kernel": "scan_bwd_kernel", "achieved": bwd_gbs, "peak": peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s",
-                         "frac": bwd_gbs / peak, "traffic": NCU_BWD_TRAFFIC_BYTES_B2 * (B / 2),
+                         "frac": bwd_gbs / peak, "traffic": NCU_BWD_TRAFFIC_BYTES_L2048 * (L / 2048),
                          "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "fwd": {"kernel": "scan_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
                                  "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
@@ -291,8 +299,8 @@ def run_gpu(args):
                     "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "path": "quick_ssm_b200.host.HostScan: pinned host buffers -> H2D -> qssm_scan_fwd/bwd -> D2H"},
-            "gpu_launches": 2 * K,
-            "gpu_launches_e2e": e2e_launches,
+            "gpu_launches": 2 * K * world,
+            "gpu_launches_e2e": e2e_launches * world,
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu:
@@ -309,6 +317,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident loop only, no bench line")
+    ap.add_argument("--seq-len", type=int, default=0, help="profiling aid: shorter L (same chains, less memory)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
