@@ -1,0 +1,160 @@
+"""Timing of the scan on the benchmark configurations other than the headline one.
+
+    python -m quick_ssm_b200.bench_configs --config cfg4 [--no-checkpoint]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        -m quick_ssm_b200.bench_configs --config cfg2 --shard seq      # time axis split over N GPUs
+        -m quick_ssm_b200.bench_configs --config cfg4 --shard batch    # batch split over N GPUs
+
+Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
+  cfg1       B=8  L=8192  D=4096 bf16                     (the headline; bench.py reports it)
+  cfg2       B=1  L=2^20  D=2048 fp16, decay close to one  (long sequence; --shard seq)
+  cfg3_scan  B=16 L=4096  D=4096 bf16 gates, fp32 y / dy   (the scan inside a 12-layer SSM stack)
+  cfg4       B=64 L=4096  D=8192 fp16                     (throughput sweep; --shard batch)
+With --shard the TOTAL problem is fixed and split over the ranks (strong scaling); the reported
+throughput is total elements over the slowest rank's device time.  One JSON line per run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .sharded import scan_sequence_sharded
+from .synth import CONFIGS, make_inputs
+
+
+def _median_ms(fn, steps, warmup, sync):
+    for _ in range(warmup):
+        fn()
+    sync()
+    out = []
+    for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return statistics.median(out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS))
+    ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
+    ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--segments", type=int, default=0, help="time segments per GPU (0 = automatic)")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = dict(CONFIGS[args.config])
+    B, L, D = cfg["B"], cfg["L"], cfg["D"]
+    total = B * L * D
+    if args.shard == "batch":
+        assert B % world == 0, "batch must divide over the ranks"
+        B //= world
+    elif args.shard == "seq":
+        assert L % world == 0, "sequence must divide over the ranks"
+        L //= world
+    dtype, out_dtype = cfg["dtype"], cfg.get("out_dtype", cfg["dtype"])
+    inp = make_inputs(B, L, D, dtype=dtype, out_dtype=out_dtype, device=dev, seed=0, decay=cfg["decay"], rank=rank)
+    x, a, b, c = inp.tensors()
+    dy = inp.dy
+    s, so = x.element_size(), dy.element_size()
+    ckpt = not args.no_checkpoint
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    res = {}
+    if args.shard == "seq" and world > 1:
+        xs, as_, bs, cs = (t.requires_grad_() for t in (x, a, b, c))
+        holder = {}
+
+        def fwd():
+            holder["y"] = scan_sequence_sharded(xs, as_, bs, cs, out_dtype=out_dtype)
+
+        def fwd_bwd():
+            fwd()
+            holder["y"].backward(dy)
+            for t in (xs, as_, bs, cs):
+                t.grad = None
+
+        res["fwd_ms"] = _median_ms(fwd, args.steps, args.warmup, sync)
+        both = _median_ms(fwd_bwd, args.steps, args.warmup, sync)
+        res["bwd_ms"] = both - res["fwd_ms"]
+    else:
+        y = torch.empty((B, L, D), dtype=out_dtype, device=dev)
+        nt = (L + _lib.tile_rows() - 1) // _lib.tile_rows()
+        tile_h = torch.empty((B, nt, D), dtype=torch.float32, device=dev) if ckpt else None
+        h_saved = None if ckpt else torch.empty((B, L, D), dtype=torch.float32, device=dev)
+        grads = [torch.empty_like(x) for _ in range(4)]
+        n_seg = args.segments
+        res["fwd_ms"] = _median_ms(lambda: _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h, h_saved=h_saved, n_seg=n_seg),
+                                   args.steps, args.warmup, sync)
+        res["bwd_ms"] = _median_ms(lambda: _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h, h_saved=h_saved,
+                                                         n_seg=n_seg), args.steps, args.warmup, sync)
+        res["fwd_inference_ms"] = _median_ms(lambda: _lib.scan_fwd(x, a, b, c, y, n_seg=n_seg),
+                                             args.steps, args.warmup, sync)
+        hbuf = grads[0]
+        res["forward_only_h_ms"] = _median_ms(lambda: _lib.scan_fwd(x, a, b, None, hbuf, n_seg=n_seg),
+                                              args.steps, args.warmup, sync)
+    _lib.check_device_status(dev)
+
+    keys = sorted(res)
+    t = torch.tensor([res[k] for k in keys], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res = dict(zip(keys, (float(v) for v in t.tolist())))
+
+    if rank == 0:
+        try:
+            with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                   "MEASURED_PEAKS.json")) as f:
+                peak = float(json.load(f)["hbm_gbs"])
+        except Exception:
+            peak = 6650.0
+        extra = 0 if ckpt else 4
+        bytes_fwd = 4 * s + so + extra
+        bytes_bwd = 8 * s + so + extra
+        step_ms = res["fwd_ms"] + res["bwd_ms"]
+        n_seg_auto = int(_lib.load().qssm_auto_segments(B, L, D, _lib.dtype_code(dtype)))
+        line = {
+            "config": args.config, "shard": args.shard, "n_gpus": world, "checkpoint": ckpt,
+            "per_rank_shape": [B, L, D], "dtype": str(dtype).replace("torch.", ""),
+            "out_dtype": str(out_dtype).replace("torch.", ""),
+            "segments_per_gpu": args.segments or n_seg_auto,
+            "gelems_fwd_bwd": total / (step_ms * 1e-3) / 1e9,
+            "algorithmic_bytes_per_elem": {"fwd": bytes_fwd, "bwd": bytes_bwd},
+            "gbs_fwd": total * bytes_fwd / (res["fwd_ms"] * 1e-3) / 1e9,
+            "gbs_bwd": total * bytes_bwd / (res["bwd_ms"] * 1e-3) / 1e9,
+            "frac_of_measured_hbm_peak": total * (bytes_fwd + bytes_bwd) / (step_ms * 1e-3) / 1e9 / (peak * world),
+            "peak_gbs_per_gpu": peak,
+            **{k: round(v, 4) for k, v in res.items()},
+        }
+        if "fwd_inference_ms" in res:
+            line["gbs_fwd_inference"] = total * (4 * s + so) / (res["fwd_inference_ms"] * 1e-3) / 1e9
+            line["gbs_forward_only_h"] = total * 4 * s / (res["forward_only_h_ms"] * 1e-3) / 1e9
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -83,6 +83,26 @@ template <typename T, int V> __device__ __forceinline__ Vec<T, V> pack(const flo
     for (int i = 0; i < V; ++i) w.v[i] = from_f<T>(in[i]);
     return w;
 }
+// two 16-bit channels: one packed conversion instead of two conversions and a merge
+template <> __device__ __forceinline__ Vec<__nv_bfloat16, 2> pack<__nv_bfloat16, 2>(const float (&in)[2]) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(in[0], in[1]);
+    Vec<__nv_bfloat16, 2> w;
+    w.v[0] = p.x;
+    w.v[1] = p.y;
+    return w;
+}
+template <> __device__ __forceinline__ Vec<__half, 2> pack<__half, 2>(const float (&in)[2]) {
+    const __half2 p = __floats2half2_rn(in[0], in[1]);
+    Vec<__half, 2> w;
+    w.v[0] = p.x;
+    w.v[1] = p.y;
+    return w;
+}
+template <> __device__ __forceinline__ void unpack<__half, 2>(const Vec<__half, 2>& w, float (&out)[2]) {
+    const float2 f = __half22float2(__halves2half2(w.v[0], w.v[1]));
+    out[0] = f.x;
+    out[1] = f.y;
+}
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers: mbarrier, bulk tensor copies
@@ -627,9 +647,12 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
     };
 
     // Gradients are stored from the stage itself, so a stage can be refilled only after the store
-    // issued from it has finished reading: prefetch distance is NS - 2.
+    // issued from it has finished reading.  With three or more stages the tile fetched at step j
+    // goes into the stage of tile j-2 (prefetch distance NS - 2, at most one store left pending);
+    // with two stages it goes into the stage of tile j-1, whose store must have drained completely.
+    const int PF = NS > 2 ? NS - 2 : 1;
     if (tma && lane == 0) {
-        for (int k = 0; k < NS - 2 && pf_left > 0; ++k) issue();
+        for (int k = 0; k < PF && pf_left > 0; ++k) issue();
     }
 
     bool ok = true;
@@ -641,7 +664,10 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
 
         if (tma) {
             if (lane == 0 && pf_left > 0) {
-                tma_wait_read<1>();  // the store of the tile before the previous one is done with its stage
+                if (NS > 2)
+                    tma_wait_read<1>();  // the store of the tile before the previous one is done with its stage
+                else
+                    tma_wait_read<0>();
                 issue();
             }
             ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
@@ -1006,21 +1032,32 @@ size_t ws_bytes_for(long long B, long long D, int n_seg) {
     return (size_t)3 * (size_t)B * (size_t)n_seg * (size_t)D * sizeof(float);
 }
 
-// Ring depth: spread the shared memory of an SM over the chains expected to be resident on it.
-int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int min_stages, int dflt_stages) {
+// Ring depth.  All chains of a launch should be resident at once: a chain runs for the whole
+// kernel, so chains that do not fit start only when others finish, and that second wave runs with
+// too few warps to keep HBM busy.  Among the depths lo..hi pick the one that wastes the fewest
+// CTA slots over all waves, preferring deeper rings on a tie.
+int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int lo, int hi) {
     const int forced = env_int("QSSM_STAGES", 0);
-    long long per_sm = (chains_total + sm_count() - 1) / sm_count();
-    const int max_res = env_int("QSSM_RESIDENT", 16);
-    if (per_sm > max_res) per_sm = max_res;
-    if (per_sm < 1) per_sm = 1;
-    const int budget = (int)((227 * 1024) / per_sm) - 1024 - fixed_bytes - MAX_STAGES * 8 - 128;
-    int ns = budget / stage_bytes;
-    if (ns > dflt_stages) ns = dflt_stages;
-    if (forced > 0) ns = forced;
-    if (ns < min_stages) ns = min_stages;
-    if (ns > MAX_STAGES) ns = MAX_STAGES;
-    while (ns > min_stages && ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 128 > 227 * 1024) --ns;
-    return ns;
+    if (forced >= lo && forced <= MAX_STAGES) return forced;
+    const long long sms = sm_count();
+    int best = lo;
+    double best_eff = -1.0;
+    for (int ns = lo; ns <= hi; ++ns) {
+        const long long smem = (long long)ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 1024;  // + per-CTA reserve
+        long long per_sm = (227 * 1024 + 1024) / smem;
+        if (per_sm < 1) continue;
+        if (per_sm > 32) per_sm = 32;
+        const long long slots = per_sm * sms;
+        const long long waves = (chains_total + slots - 1) / slots;
+        const double eff = (double)chains_total / (double)(waves * slots);
+        // a single wave is all that matters; beyond that compare slot efficiency
+        const double score = waves == 1 ? 1.0 : eff;
+        if (score >= best_eff) {
+            best_eff = score;
+            best = ns;
+        }
+    }
+    return best;
 }
 
 int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* status) {
@@ -1381,7 +1418,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     const int hrow = chans * 4;
     const int h_tile = saved ? (TB + 1) * hrow : (TB / TS) * hrow;
     const int stage = 4 * TB * chans * es + TB * chans * eo + ((h_tile + 127) / 128) * 128;
-    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 3, 3);
+    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 2, 3);
     const int smem = bp.g.n_stages * stage + MAX_STAGES * 8;
     return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
         using Tin = decltype(tin);
