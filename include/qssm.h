@@ -94,8 +94,11 @@ int qssm_auto_segments(int64_t B, int64_t L, int64_t D, int in_dtype);
  *   h_last  [B,D] fp32: h(L-1)
  * Optional input
  *   h_in    [B,D] fp32: state before t=0 (sequence shards, streaming)
- * n_seg: 0 = automatic, otherwise the number of time segments to run in parallel
- *        (needs ws; results are identical within fp32 rounding for every value).
+ * n_seg: 0 = automatic, k > 0 = k time segments run in parallel (needs ws; results are identical
+ *        within fp32 rounding for every value), -k = k segments whose aggregates are already in
+ *        ws, left there by qssm_scan_aggregate_fwd called with the same shape, dtype and n_seg = k
+ *        (sequence shards: the aggregate pass that feeds the exchange is not repeated).
+ *        qssm_scan_bwd takes the same three forms, paired with qssm_scan_aggregate_bwd.
  */
 int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, void* y,
                   float* h_saved, float* tile_h, const float* h_in, float* h_last,

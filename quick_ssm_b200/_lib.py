@@ -166,13 +166,15 @@ def workspace(B: int, L: int, D: int, code: int, n_seg: int, device) -> Optional
 # ---------------------------------------------------------------------------------------------
 # thin call wrappers (arguments already validated / laid out by the caller)
 # ---------------------------------------------------------------------------------------------
-def scan_fwd(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None, n_seg: int = 0) -> None:
-    dev = _require_cuda(x, a, b, c, y, h_saved, tile_h, h_in, h_last)
+def scan_fwd(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None, n_seg: int = 0, ws=None) -> None:
+    """``n_seg`` < 0 with ``ws`` from ``aggregate_fwd``: reuse the segment aggregates already in ``ws``."""
+    dev = _require_cuda(x, a, b, c, y, h_saved, tile_h, h_in, h_last, ws)
     B, L, D = x.shape
     check_device_status(dev)
     with torch.cuda.device(dev):
         code_in, code_out = dtype_code(x.dtype), dtype_code(y.dtype)
-        ws = workspace(B, L, D, code_in, n_seg, dev)
+        if ws is None:
+            ws = workspace(B, L, D, code_in, abs(n_seg), dev)
         sb, sl = _blds(x)
         ob, ol = _blds(y)
         rc = load().qssm_scan_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(y), _ptr(h_saved), _ptr(tile_h),
@@ -203,13 +205,15 @@ def scan_fwd_static_ws(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h
 
 
 def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=None, g_in=None, g_first=None,
-             n_seg: int = 0) -> None:
-    dev = _require_cuda(x, a, b, c, dy, dx, da, db, dc, h_saved, tile_h, h_in, g_in, g_first)
+             n_seg: int = 0, ws=None) -> None:
+    """``n_seg`` < 0 with ``ws`` from ``aggregate_bwd``: reuse the segment aggregates already in ``ws``."""
+    dev = _require_cuda(x, a, b, c, dy, dx, da, db, dc, h_saved, tile_h, h_in, g_in, g_first, ws)
     B, L, D = x.shape
     check_device_status(dev)
     with torch.cuda.device(dev):
         code_in, code_out = dtype_code(x.dtype), dtype_code(dy.dtype)
-        ws = workspace(B, L, D, code_in, n_seg, dev)
+        if ws is None:
+            ws = workspace(B, L, D, code_in, abs(n_seg), dev)
         sb, sl = _blds(x)
         gb, gl = _blds(dy)
         rc = load().qssm_scan_bwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(dy), _ptr(h_saved), _ptr(tile_h),
@@ -219,13 +223,18 @@ def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=
     _rc(rc, "qssm_scan_bwd")
 
 
-def aggregate_fwd(x, a, b, A, H, *, n_seg: int = 0) -> None:
-    dev = _require_cuda(x, a, b, A, H)
+def auto_segments(B: int, L: int, D: int, dtype: torch.dtype) -> int:
+    return int(load().qssm_auto_segments(B, L, D, dtype_code(dtype)))
+
+
+def aggregate_fwd(x, a, b, A, H, *, n_seg: int = 0, ws=None) -> None:
+    dev = _require_cuda(x, a, b, A, H, ws)
     B, L, D = x.shape
     check_device_status(dev)
     with torch.cuda.device(dev):
         code = dtype_code(x.dtype)
-        ws = workspace(B, L, D, code, n_seg, dev)
+        if ws is None:
+            ws = workspace(B, L, D, code, n_seg, dev)
         sb, sl = _blds(x)
         rc = load().qssm_scan_aggregate_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(A), _ptr(H), _ptr(ws),
                                             0 if ws is None else ws.numel(), B, L, D, sb, sl, code, int(n_seg),
@@ -233,13 +242,14 @@ def aggregate_fwd(x, a, b, A, H, *, n_seg: int = 0) -> None:
     _rc(rc, "qssm_scan_aggregate_fwd")
 
 
-def aggregate_bwd(a, c, dy, P, Q, *, n_seg: int = 0) -> None:
-    dev = _require_cuda(a, c, dy, P, Q)
+def aggregate_bwd(a, c, dy, P, Q, *, n_seg: int = 0, ws=None) -> None:
+    dev = _require_cuda(a, c, dy, P, Q, ws)
     B, L, D = a.shape
     check_device_status(dev)
     with torch.cuda.device(dev):
         code, code_dy = dtype_code(a.dtype), dtype_code(dy.dtype)
-        ws = workspace(B, L, D, code, n_seg, dev)
+        if ws is None:
+            ws = workspace(B, L, D, code, n_seg, dev)
         sb, sl = _blds(a)
         gb, gl = _blds(dy)
         rc = load().qssm_scan_aggregate_bwd(_ptr(a), _ptr(c), _ptr(dy), _ptr(P), _ptr(Q), _ptr(ws),

@@ -999,12 +999,14 @@ struct Plan {
 };
 
 // Channels per lane.  Two channels per lane halve the shared-memory and copy-engine instructions
-// per element and measured faster whenever they still leave a couple of chains per SM; narrow
-// strips (V = 1) double the number of independent warps for small batch x channel counts.
-int pick_v(long long B, long long D) {
+// per element, so one warp moves twice the bytes; narrow strips (V = 1) are for channel counts
+// that would leave half of a wide strip empty, or for launches with too few chains to give
+// every SM two warps even after the time axis has been segmented.
+int pick_v(long long B, long long D, int n_seg) {
     const int forced = env_int("QSSM_V", 0);
     if (forced == 1 || forced == 2) return forced;
-    const long long chains_v2 = B * ((D + 63) / 64);
+    if (D <= 32) return 1;
+    const long long chains_v2 = B * ((D + 63) / 64) * (n_seg < 1 ? 1 : n_seg);
     return chains_v2 >= 2ll * sm_count() ? 2 : 1;
 }
 int pick_tb() {
@@ -1012,17 +1014,19 @@ int pick_tb() {
     return forced == 16 || forced == 32 ? forced : 16;
 }
 
-long long n_chains(long long B, long long D, int V) { return B * ((D + 32 * V - 1) / (32 * V)); }
 
-// Segment count: split time only when batch x channels gives fewer chains than SMs.
+// Segment count.  Cutting the time axis costs an extra read of the tensors the carry depends on
+// (8 instead of 5 tensor passes forward, 12 instead of 9 backward), so it pays only when batch x
+// channels alone leaves most of the GPU idle: fewer than two wide chains per SM.
 int auto_segments(long long B, long long L, long long D, int in_dtype) {
     if (B <= 0 || L <= 0 || D <= 0 || dtype_size(in_dtype) == 0) return 1;
-    const long long chains = n_chains(B, D, 1);
-    if (chains >= 128) return 1;
-    long long want = (512 + chains - 1) / chains;
-    const long long max_by_len = L / (8 * 32);  // at least 256 rows per segment
+    const long long chains = B * ((D + 63) / 64);
+    const long long sms = sm_count();
+    if (chains >= 2 * sms) return 1;
+    long long want = (4 * sms + chains - 1) / chains;
+    const long long max_by_len = L / 256;  // at least 256 rows per segment
     if (want > max_by_len) want = max_by_len;
-    if (want < 1) want = 1;
+    if (want < 2) want = 1;
     if (want > 4096) want = 4096;
     return (int)want;
 }
@@ -1061,16 +1065,16 @@ int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int lo
 }
 
 int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* status) {
-    pl.V = pick_v(B, D);
+    if (n_seg < 1) n_seg = 1;
+    long long seg_rows = (L + n_seg - 1) / n_seg;
+    seg_rows = ((seg_rows + 31) / 32) * 32;  // whole tiles for either tile height
+    n_seg = (int)((L + seg_rows - 1) / seg_rows);
+    pl.V = pick_v(B, D, n_seg);
     pl.TB = pick_tb();
     const int chans = 32 * pl.V;
     Geom& g = pl.g;
     g.B = B; g.L = L; g.D = D;
     g.n_dtiles = (int)((D + chans - 1) / chans);
-    if (n_seg < 1) n_seg = 1;
-    long long seg_rows = (L + n_seg - 1) / n_seg;
-    seg_rows = ((seg_rows + 31) / 32) * 32;  // whole tiles for either tile height
-    n_seg = (int)((L + seg_rows - 1) / seg_rows);
     g.n_seg = n_seg;
     g.seg_rows = (int)seg_rows;
     g.status = status;
@@ -1167,6 +1171,7 @@ int run_aggregate(bool reverse, const void* t0, const void* t1, const void* t2, 
 
 int resolve_segments(int n_seg_req, long long B, long long L, long long D, int in_dtype, const void* ws,
                      size_t ws_bytes, int* n_seg_out) {
+    if (n_seg_req < 0) n_seg_req = -n_seg_req;  // "aggregates already in ws": same count, same layout
     int n_seg = n_seg_req > 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
     if (n_seg > 1) {
         // make_plan may lower the count after rounding segments to whole tiles; size for the request
@@ -1273,9 +1278,11 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     const float* seeds = h_in;
     if (n_seg > 1) {
         SegScratch sc = carve(ws, B, n_seg, D);
-        rc = run_aggregate(false, x, a, b, sc.A, sc.H, pl, in_stride_b, in_stride_l, in_stride_b, in_stride_l,
-                           in_dtype, in_dtype, stream);
-        if (rc) return rc;
+        if (n_seg_req >= 0) {  // negative: qssm_scan_aggregate_fwd has already left them in ws
+            rc = run_aggregate(false, x, a, b, sc.A, sc.H, pl, in_stride_b, in_stride_l, in_stride_b, in_stride_l,
+                               in_dtype, in_dtype, stream);
+            if (rc) return rc;
+        }
         const long long n = B * D;
         seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(sc.A, sc.H, h_in, sc.seeds, nullptr,
                                                                           nullptr, B, n_seg, D, 0);
@@ -1329,7 +1336,7 @@ int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const v
     int rc = check_common(B, L, D, in_dtype, out_dtype);
     if (rc) return rc;
     // Scratch the segmented scan would need; refuse rather than quietly run unsegmented.
-    const int n_seg = n_seg_req > 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
+    const int n_seg = n_seg_req != 0 ? (n_seg_req < 0 ? -n_seg_req : n_seg_req) : auto_segments(B, L, D, in_dtype);
     const size_t need = ws_bytes_for(B, D, n_seg);
     if (need > (size_t)QSSM_STATIC_WS_BYTES) return QSSM_E_STATIC_WS;
     void* ws = nullptr;
@@ -1372,9 +1379,11 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     const float* seeds = g_in;
     if (n_seg > 1) {
         SegScratch sc = carve(ws, B, n_seg, D);
-        rc = run_aggregate(true, a, c, dy, sc.A, sc.H, pl, in_stride_b, in_stride_l, dy_stride_b, dy_stride_l,
-                           in_dtype, out_dtype, stream);
-        if (rc) return rc;
+        if (n_seg_req >= 0) {  // negative: qssm_scan_aggregate_bwd has already left them in ws
+            rc = run_aggregate(true, a, c, dy, sc.A, sc.H, pl, in_stride_b, in_stride_l, dy_stride_b, dy_stride_l,
+                               in_dtype, out_dtype, stream);
+            if (rc) return rc;
+        }
         const long long n = B * D;
         seg_carry_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(sc.A, sc.H, g_in, sc.seeds, nullptr,
                                                                           nullptr, B, n_seg, D, 1);

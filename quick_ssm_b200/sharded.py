@@ -25,30 +25,59 @@ from .scan_interface import _addressable, _kernel_out_dtype, _n_tiles, _prepare_
 
 
 class CudaShardOps:
-    """The five device operations of a sequence shard, through the C ABI."""
+    """The five device operations of a sequence shard, through the C ABI.
+
+    When the local shard is itself cut into time segments, the aggregate pass leaves the
+    per-segment aggregates in a workspace that the scan call right after it reuses, so the
+    tensors the carry depends on are read once for both purposes."""
+
+    def __init__(self):
+        self._ws_fwd = None  # (workspace, segments) left by aggregate_fwd for the next forward
+        self._ws_bwd = None
+
+    @staticmethod
+    def _segments(t):
+        B, L, D = t.shape
+        k = _lib.auto_segments(B, L, D, t.dtype)
+        ws = torch.empty(3 * B * k * D * 4, dtype=torch.uint8, device=t.device) if k > 1 else None
+        return k, ws
 
     def aggregate_fwd(self, x, a, b):
         B, L, D = x.shape
         A = torch.empty((B, D), dtype=torch.float32, device=x.device)
         H = torch.empty_like(A)
-        _lib.aggregate_fwd(x, a, b, A, H)
+        k, ws = self._segments(x)
+        _lib.aggregate_fwd(x, a, b, A, H, n_seg=k, ws=ws)
+        self._ws_fwd = (ws, k) if k > 1 else None
         return A, H
 
     def aggregate_bwd(self, a, c, dy):
         B, L, D = a.shape
         P = torch.empty((B, D), dtype=torch.float32, device=a.device)
         Q = torch.empty_like(P)
-        _lib.aggregate_bwd(a, c, dy, P, Q)
+        k, ws = self._segments(a)
+        _lib.aggregate_bwd(a, c, dy, P, Q, n_seg=k, ws=ws)
+        self._ws_bwd = (ws, k) if k > 1 else None
         return P, Q
 
     def fold(self, A, H, upto: int, reverse: bool):
         return _lib.carry_fold(A, H, upto, reverse=reverse)
 
     def forward(self, x, a, b, c, y, tile_h, h_in):
-        _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h, h_in=h_in)
+        if self._ws_fwd is not None:
+            ws, k = self._ws_fwd
+            self._ws_fwd = None
+            _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h, h_in=h_in, n_seg=-k, ws=ws)
+        else:
+            _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h, h_in=h_in)
 
     def backward(self, x, a, b, c, dy, tile_h, g_in, grads):
-        _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h, g_in=g_in)
+        if self._ws_bwd is not None:
+            ws, k = self._ws_bwd
+            self._ws_bwd = None
+            _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h, g_in=g_in, n_seg=-k, ws=ws)
+        else:
+            _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h, g_in=g_in)
 
 
 def _gather(pair, group):
@@ -61,25 +90,47 @@ def _gather(pair, group):
     return full[:, 0].contiguous(), full[:, 1].contiguous()
 
 
+def shard_forward(ops, group, xs, as_, bs, cs, k_out, keep_boundaries: bool):
+    """Forward of one sequence shard (no autograd): returns ``(y, tile_h or None)``."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    B, L, D = xs.shape
+    if rank == world - 1:  # nobody comes after the last shard: identity aggregate, no read
+        A = torch.ones((B, D), dtype=torch.float32, device=xs.device)
+        H = torch.zeros_like(A)
+    else:
+        A, H = ops.aggregate_fwd(xs, as_, bs)
+    A_all, H_all = _gather((A, H), group)
+    h_in = ops.fold(A_all, H_all, rank, False)
+    y = torch.empty((B, L, D), dtype=k_out, device=xs.device)
+    tile_h = torch.empty((B, _n_tiles(L), D), dtype=torch.float32, device=xs.device) if keep_boundaries else None
+    ops.forward(xs, as_, bs, cs, y, tile_h, h_in)
+    return y, tile_h
+
+
+def shard_backward(ops, group, xs, as_, bs, cs, dy, tile_h):
+    """Backward of one sequence shard (no autograd): returns ``[dx, da, db, dc]`` in the input dtype."""
+    rank = dist.get_rank(group)
+    B, L, D = xs.shape
+    if rank == 0:  # nobody comes before the first shard
+        P = torch.ones((B, D), dtype=torch.float32, device=xs.device)
+        Q = torch.zeros_like(P)
+    else:
+        P, Q = ops.aggregate_bwd(as_, cs, dy)
+    P_all, Q_all = _gather((P, Q), group)
+    g_in = ops.fold(P_all, Q_all, rank, True)
+    grads = [torch.empty(xs.shape, dtype=xs.dtype, device=xs.device) for _ in range(4)]
+    ops.backward(xs, as_, bs, cs, dy, tile_h, g_in, grads)
+    return grads
+
+
 class _SequenceShardedScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, a, b, c, group, out_dtype, ops):
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
         in_dtypes = (x.dtype, a.dtype, b.dtype, c.dtype)
         xs, as_, bs, cs = _prepare_inputs(x, a, b, c)
-        B, L, D = xs.shape
-        if rank == world - 1:  # nobody comes after the last shard: identity aggregate, no read
-            A = torch.ones((B, D), dtype=torch.float32, device=xs.device)
-            H = torch.zeros_like(A)
-        else:
-            A, H = ops.aggregate_fwd(xs, as_, bs)
-        A_all, H_all = _gather((A, H), group)
-        h_in = ops.fold(A_all, H_all, rank, False)
         k_out = _kernel_out_dtype(xs.dtype, out_dtype)
-        y = torch.empty((B, L, D), dtype=k_out, device=xs.device)
         needs_grad = any(ctx.needs_input_grad[:4])
-        tile_h = torch.empty((B, _n_tiles(L), D), dtype=torch.float32, device=xs.device) if needs_grad else None
-        ops.forward(xs, as_, bs, cs, y, tile_h, h_in)
+        y, tile_h = shard_forward(ops, group, xs, as_, bs, cs, k_out, needs_grad)
         if needs_grad:
             ctx.save_for_backward(xs, as_, bs, cs, tile_h)
         ctx.group, ctx.ops, ctx.k_out, ctx.in_dtypes = group, ops, k_out, in_dtypes
@@ -88,19 +139,8 @@ class _SequenceShardedScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         xs, as_, bs, cs, tile_h = ctx.saved_tensors
-        group, ops = ctx.group, ctx.ops
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
         dy = _addressable(grad_output if grad_output.dtype == ctx.k_out else grad_output.to(ctx.k_out))
-        B, L, D = xs.shape
-        if rank == 0:  # nobody comes before the first shard
-            P = torch.ones((B, D), dtype=torch.float32, device=xs.device)
-            Q = torch.zeros_like(P)
-        else:
-            P, Q = ops.aggregate_bwd(as_, cs, dy)
-        P_all, Q_all = _gather((P, Q), group)
-        g_in = ops.fold(P_all, Q_all, rank, True)
-        grads = [torch.empty(xs.shape, dtype=xs.dtype, device=xs.device) for _ in range(4)]
-        ops.backward(xs, as_, bs, cs, dy, tile_h, g_in, grads)
+        grads = shard_backward(ctx.ops, ctx.group, xs, as_, bs, cs, dy, tile_h)
         return tuple(g.to(dt) for g, dt in zip(grads, ctx.in_dtypes)) + (None, None, None)
 
 

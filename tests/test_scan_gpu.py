@@ -255,3 +255,35 @@ def test_kernel_level_entry_points():
             assert_close_f32(g, r, name)
     e = torch.empty(2, 0, 4, device=DEV)
     assert block_scan_forward_3d(e, e, e)[1].shape == e.shape
+
+
+def test_segment_aggregates_are_reused_by_the_scan():
+    """n_seg = -k: the scan takes the per-segment aggregates an aggregate call left in the workspace."""
+    inp = make_inputs(2, 3000, 70, dtype=torch.bfloat16, seed=12).to(DEV)
+    x, a, b, c = inp.tensors()
+    B, L, D = x.shape
+    k = 6
+    h0 = torch.randn(B, D, device=DEV)
+    ref = torch.empty_like(x)
+    _lib.scan_fwd(x, a, b, c, ref, h_in=h0, n_seg=k)
+    ws = torch.empty(3 * B * k * D * 4, dtype=torch.uint8, device=DEV)
+    A = torch.empty(B, D, device=DEV)
+    H = torch.empty(B, D, device=DEV)
+    _lib.aggregate_fwd(x, a, b, A, H, n_seg=k, ws=ws)
+    got = torch.empty_like(x)
+    _lib.scan_fwd(x, a, b, c, got, h_in=h0, n_seg=-k, ws=ws)
+    assert torch.equal(got, ref)
+    # backward twin
+    th = torch.empty(B, (L + 15) // 16, D, device=DEV)
+    _lib.scan_fwd(x, a, b, c, ref, tile_h=th, h_in=h0)
+    g0 = torch.randn(B, D, device=DEV)
+    want = [torch.empty_like(x) for _ in range(4)]
+    _lib.scan_bwd(x, a, b, c, inp.dy, *want, tile_h=th, g_in=g0, n_seg=k)
+    P = torch.empty(B, D, device=DEV)
+    Q = torch.empty(B, D, device=DEV)
+    _lib.aggregate_bwd(a, c, inp.dy, P, Q, n_seg=k, ws=ws)
+    have = [torch.empty_like(x) for _ in range(4)]
+    _lib.scan_bwd(x, a, b, c, inp.dy, *have, tile_h=th, g_in=g0, n_seg=-k, ws=ws)
+    _lib.check_device_status(synchronize=True)
+    for w, h in zip(want, have):
+        assert torch.equal(w, h)
