@@ -166,6 +166,41 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
                  "r"(src), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
+// Same copies with an L2 eviction-priority hint (policy from createpolicy).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                                 int c2, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2,
+                                                  uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_ld(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                       bool hint, uint64_t pol) {
+    if (hint)
+        tma_load_3d_hint(dst, map, bar, c0, c1, c2, pol);
+    else
+        tma_load_3d(dst, map, bar, c0, c1, c2);
+}
+__device__ __forceinline__ void tma_st(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, bool hint,
+                                       uint64_t pol) {
+    if (hint)
+        tma_store_3d_hint(map, src, c0, c1, c2, pol);
+    else
+        tma_store_3d(map, src, c0, c1, c2);
+}
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void tma_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -188,8 +223,11 @@ struct Geom {
     int n_dtiles;   // ceil(D / channels per warp)
     int n_seg;      // time segments
     int seg_rows;   // rows per segment, a multiple of the tile rows
+    long long n_chains;  // B * n_seg * n_dtiles; CTAs take chains blockIdx.x, + gridDim.x, ...
     int n_stages;   // ring depth
     int use_tma;    // 0: guarded per-lane accesses
+    int l2_hint;    // bit 0: loads evict-first, bit 1: stores evict-first
+    int n_out;      // forward: output staging buffers in the ring (2..4)
     int* status;    // may be NULL
 };
 
@@ -273,9 +311,8 @@ struct Chain {
     int seg, n_tiles;
     bool empty;
 };
-__device__ __forceinline__ Chain chain_of_block(const Geom& g, int chans_per_warp, int tile_rows) {
+__device__ __forceinline__ Chain chain_of(const Geom& g, long long id, int chans_per_warp, int tile_rows) {
     Chain c;
-    const long long id = blockIdx.x;
     const long long dt = id % g.n_dtiles;
     const long long rest = id / g.n_dtiles;
     c.seg = static_cast<int>(rest % g.n_seg);
@@ -365,14 +402,32 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
     const Geom& g = p.g;
     const int NS = g.n_stages;
     unsigned char* const outbuf = smem + NS * STAGE;
-    const uint32_t bars = smem_u32(outbuf + 2 * OUTBUF);
+    const int NOUT = g.n_out;
+    const uint32_t bars = smem_u32(outbuf + NOUT * OUTBUF);
     const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT, TB);
-    if (ch.empty) return;
-    const long long d_lane = ch.d0 + (long long)lane * V;
     const bool tma = g.use_tma != 0;
+    const bool ld_hint = (g.l2_hint & 1) != 0, st_hint = (g.l2_hint & 2) != 0;
+    const uint64_t pol = l2_policy_evict_first();
+
+    if (tma) {
+        if (lane == 0) {
+            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+
+    bool ok = true;
+    RingPos pf{0, 0};   // next stage to fill
+    RingPos cur{0, 0};  // stage being scanned
+    // A CTA walks chains blockIdx.x, blockIdx.x + gridDim.x, ...: the grid bounds how many chains
+    // stream at once, independently of how many there are.
+    for (long long chain_id = blockIdx.x; chain_id < g.n_chains; chain_id += gridDim.x) {
+    const Chain ch = chain_of(g, chain_id, DT, TB);
+    if (ch.empty) continue;
+    const long long d_lane = ch.d0 + (long long)lane * V;
 
     float h[V];
 #pragma unroll
@@ -386,16 +441,7 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
     float* th_dst = nullptr;  // tile_h row of the next 16-row batch, this lane's channels
     if (p.tile_h != nullptr) th_dst = p.tile_h + (ch.b * ((g.L + TS - 1) / TS) + ch.t_begin / TS) * g.D + d_lane;
 
-    if (tma) {
-        if (lane == 0) {
-            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
-            fence_barrier_init();
-        }
-        __syncwarp();
-    }
-
     const int c0 = (int)ch.d0, c2 = (int)ch.b;
-    RingPos pf{0, 0};  // next stage to fill
     int pf_row = (int)ch.t_begin;
     int pf_left = ch.n_tiles;
     auto issue = [&]() {  // lane 0 only: loads of the next tile into stage pf.s
@@ -403,10 +449,10 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
         const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
         mbar_expect_tx(bar, STAGE);
-        tma_load_3d(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2);
-        if (HAS_C) tma_load_3d(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2);
+        tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2, ld_hint, pol);
+        if (HAS_C) tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2, ld_hint, pol);
         pf.advance(NS);
         pf_row += TB;
         --pf_left;
@@ -416,18 +462,21 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
         for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
     }
 
-    bool ok = true;
-    RingPos cur{0, 0};
     long long t0 = ch.t_begin;
+    int oslot = 0;
     for (int j = 0; j < ch.n_tiles; ++j, t0 += TB) {
         unsigned char* st = smem + cur.s * STAGE;
-        unsigned char* ob = outbuf + (j & 1) * OUTBUF;
+        unsigned char* ob = outbuf + oslot * OUTBUF;
+        if (++oslot == NOUT) oslot = 0;
         const int nrows = (int)((ch.t_end - t0) < TB ? (ch.t_end - t0) : TB);
 
         if (tma) {
             if (lane == 0) {
                 if (pf_left > 0) issue();
-                tma_wait_read<1>();  // the store issued two tiles ago has finished reading `ob`
+                // the store issued NOUT tiles ago has finished reading `ob`
+                if (NOUT == 2) tma_wait_read<1>();
+                else if (NOUT == 3) tma_wait_read<2>();
+                else tma_wait_read<3>();
             }
             ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
             ok = __all_sync(0xffffffffu, ok);
@@ -466,8 +515,8 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                tma_store_3d(&p.y.map, smem_u32(ob), c0, (int)t0, c2);
-                if (SAVE_H) tma_store_3d(&p.hs.map, smem_u32(ob + OUT_TILE), c0, (int)t0, c2);
+                tma_st(&p.y.map, smem_u32(ob), c0, (int)t0, c2, st_hint, pol);
+                if (SAVE_H) tma_st(&p.hs.map, smem_u32(ob + OUT_TILE), c0, (int)t0, c2, st_hint, pol);
                 tma_commit();
             }
         } else {
@@ -478,17 +527,21 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
         cur.advance(NS);
     }
 
-    if (tma && lane == 0) tma_wait_all();
-    if (!ok) {
-        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
-        return;
-    }
+    if (!ok) break;
     if (p.h_last != nullptr && ch.seg == g.n_seg - 1) {
         float* dst = p.h_last + ch.b * g.D;
 #pragma unroll
         for (int i = 0; i < V; ++i)
             if (d_lane + i < g.D) dst[d_lane + i] = h[i];
     }
+    if (tma) {  // the stores of this chain have read their buffers before the next chain reuses them
+        if (lane == 0) tma_wait_read<0>();
+        __syncwarp();
+    }
+    }  // chains
+
+    if (tma && lane == 0) tma_wait_all();
+    if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -597,11 +650,26 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
     const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT, TB);
-    if (ch.empty) return;
-    const long long d_lane = ch.d0 + (long long)lane * V;
     const bool tma = g.use_tma != 0;
+    const bool ld_hint = (g.l2_hint & 1) != 0, st_hint = (g.l2_hint & 2) != 0;
+    const uint64_t pol = l2_policy_evict_first();
     const long long tiles_per_b = (g.L + TS - 1) / TS;
+
+    if (tma) {
+        if (lane == 0) {
+            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+
+    bool ok = true;
+    RingPos pf{0, 0};
+    RingPos cur{0, 0};
+    for (long long chain_id = blockIdx.x; chain_id < g.n_chains; chain_id += gridDim.x) {
+    const Chain ch = chain_of(g, chain_id, DT, TB);
+    if (ch.empty) continue;
+    const long long d_lane = ch.d0 + (long long)lane * V;
 
     float G[V];
 #pragma unroll
@@ -614,17 +682,8 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
     }
     const float* h_in_lane = (SAVED_H && p.h_in != nullptr) ? p.h_in + ch.b * g.D + d_lane : nullptr;
 
-    if (tma) {
-        if (lane == 0) {
-            for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
-            fence_barrier_init();
-        }
-        __syncwarp();
-    }
-
     const int c0 = (int)ch.d0, c2 = (int)ch.b;
     // tiles are walked from the last to the first
-    RingPos pf{0, 0};
     int pf_row = (int)(ch.t_begin + (long long)(ch.n_tiles - 1) * TB);
     int pf_left = ch.n_tiles;
     auto issue = [&]() {
@@ -632,15 +691,15 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
         const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
         mbar_expect_tx(bar, 4 * IN_TILE + DY_TILE + H_TILE);
-        tma_load_3d(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + OFF_DY, &p.dy.map, bar, c0, pf_row, c2);
+        tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + OFF_DY, &p.dy.map, bar, c0, pf_row, c2, ld_hint, pol);
         if (SAVED_H)
-            tma_load_3d(st + OFF_H, &p.hsrc.map, bar, c0, pf_row - 1, c2);  // row -1 reads zero fill
+            tma_ld(st + OFF_H, &p.hsrc.map, bar, c0, pf_row - 1, c2, ld_hint, pol);  // row -1 reads zero fill
         else
-            tma_load_3d(st + OFF_H, &p.hsrc.map, bar, c0, pf_row / TS, c2);
+            tma_ld(st + OFF_H, &p.hsrc.map, bar, c0, pf_row / TS, c2, ld_hint, pol);
         pf.advance(NS);
         pf_row -= TB;
         --pf_left;
@@ -655,8 +714,6 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
         for (int k = 0; k < PF && pf_left > 0; ++k) issue();
     }
 
-    bool ok = true;
-    RingPos cur{0, 0};
     long long t0 = ch.t_begin + (long long)(ch.n_tiles - 1) * TB;
     for (int j = 0; j < ch.n_tiles; ++j, t0 -= TB) {
         unsigned char* st = smem + cur.s * STAGE;
@@ -711,10 +768,10 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
             __syncwarp();
             if (lane == 0) {
                 const uint32_t sst = smem_base + cur.s * STAGE;
-                tma_store_3d(&p.dx.map, sst + 0 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.da.map, sst + 1 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.db.map, sst + 2 * IN_TILE, c0, (int)t0, c2);
-                tma_store_3d(&p.dc.map, sst + 3 * IN_TILE, c0, (int)t0, c2);
+                tma_st(&p.dx.map, sst + 0 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.da.map, sst + 1 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.db.map, sst + 2 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.dc.map, sst + 3 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
                 tma_commit();
             }
         } else {
@@ -727,17 +784,21 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
         cur.advance(NS);
     }
 
-    if (tma && lane == 0) tma_wait_all();
-    if (!ok) {
-        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
-        return;
-    }
+    if (!ok) break;
     if (p.g_first != nullptr && ch.seg == 0) {
         float* dst = p.g_first + ch.b * g.D;
 #pragma unroll
         for (int i = 0; i < V; ++i)
             if (d_lane + i < g.D) dst[d_lane + i] = G[i];
     }
+    if (tma) {  // the stores of this chain have read their stages before the next chain refills them
+        if (lane == 0) tma_wait_read<0>();
+        __syncwarp();
+    }
+    }  // chains
+
+    if (tma && lane == 0) tma_wait_all();
+    if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -759,22 +820,9 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
     const uint32_t smem_base = smem_u32(smem);
 
     const int lane = threadIdx.x;
-    const Chain ch = chain_of_block(g, DT, TB);
-    const long long d_lane = ch.d0 + (long long)lane * V;
-    float* const outA = p.A + (ch.b * g.n_seg + ch.seg) * g.D;
-    float* const outH = p.H + (ch.b * g.n_seg + ch.seg) * g.D;
-    if (ch.empty) {  // identity
-#pragma unroll
-        for (int i = 0; i < V; ++i)
-            if (d_lane + i < g.D) { outA[d_lane + i] = 1.f; outH[d_lane + i] = 0.f; }
-        return;
-    }
     const bool tma = g.use_tma != 0;
-
-    float A[V], H[V];
-#pragma unroll
-    for (int i = 0; i < V; ++i) { A[i] = 1.f; H[i] = 0.f; }
-
+    const bool ld_hint = (g.l2_hint & 1) != 0;
+    const uint64_t pol = l2_policy_evict_first();
     if (tma) {
         if (lane == 0) {
             for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
@@ -782,8 +830,26 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
         }
         __syncwarp();
     }
-    const int c0 = (int)ch.d0, c2 = (int)ch.b;
+    bool ok = true;
     RingPos pf{0, 0};
+    RingPos cur{0, 0};
+    for (long long chain_id = blockIdx.x; chain_id < g.n_chains; chain_id += gridDim.x) {
+    const Chain ch = chain_of(g, chain_id, DT, TB);
+    const long long d_lane = ch.d0 + (long long)lane * V;
+    float* const outA = p.A + (ch.b * g.n_seg + ch.seg) * g.D;
+    float* const outH = p.H + (ch.b * g.n_seg + ch.seg) * g.D;
+    if (ch.empty) {  // identity
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            if (d_lane + i < g.D) { outA[d_lane + i] = 1.f; outH[d_lane + i] = 0.f; }
+        continue;
+    }
+
+    float A[V], H[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { A[i] = 1.f; H[i] = 0.f; }
+
+    const int c0 = (int)ch.d0, c2 = (int)ch.b;
     int pf_row = (int)(REVERSE ? ch.t_begin + (long long)(ch.n_tiles - 1) * TB : ch.t_begin);
     int pf_left = ch.n_tiles;
     auto issue = [&]() {
@@ -791,9 +857,9 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
         const uint32_t bar = bars + 8 * pf.s;
         fence_proxy_async();
         mbar_expect_tx(bar, STAGE);
-        tma_load_3d(st + 0 * IN_TILE, &p.t0.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 1 * IN_TILE, &p.t1.map, bar, c0, pf_row, c2);
-        tma_load_3d(st + 2 * IN_TILE, &p.t2.map, bar, c0, pf_row, c2);
+        tma_ld(st + 0 * IN_TILE, &p.t0.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 1 * IN_TILE, &p.t1.map, bar, c0, pf_row, c2, ld_hint, pol);
+        tma_ld(st + 2 * IN_TILE, &p.t2.map, bar, c0, pf_row, c2, ld_hint, pol);
         pf.advance(NS);
         pf_row += REVERSE ? -TB : TB;
         --pf_left;
@@ -801,8 +867,6 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
     if (tma && lane == 0) {
         for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
     }
-    bool ok = true;
-    RingPos cur{0, 0};
     long long t0 = REVERSE ? ch.t_begin + (long long)(ch.n_tiles - 1) * TB : ch.t_begin;
     for (int j = 0; j < ch.n_tiles; ++j, t0 += (REVERSE ? -TB : TB)) {
         unsigned char* st = smem + cur.s * STAGE;
@@ -848,13 +912,12 @@ __global__ void __launch_bounds__(32) scan_agg_kernel(const __grid_constant__ Ag
         __syncwarp();
         cur.advance(NS);
     }
-    if (!ok) {
-        if (lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
-        return;
-    }
+    if (!ok) break;
 #pragma unroll
     for (int i = 0; i < V; ++i)
         if (d_lane + i < g.D) { outA[d_lane + i] = A[i]; outH[d_lane + i] = H[i]; }
+    }  // chains
+    if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -995,8 +1058,24 @@ int sm_count() {
 struct Plan {
     Geom g;
     int V, TB;
-    long long chains;  // grid size
+    long long chains;  // chains of the launch
+    long long grid;    // CTAs (= chains streaming at the same time)
 };
+
+// How many chains stream at once.  Measured on B200 (bf16/fp16, 128-byte strips): throughput rises
+// with the number of resident chains up to about 3.5 per SM (512 in all) and then falls again -
+// at 7 per SM the backward moves 17 % and the forward 7 % fewer bytes per second; the read-mostly
+// forward peaks at exactly four per SM (one warp on every scheduler).  Launches with more chains
+// than that therefore run them in equal rounds on a grid near the sweet spot; a launch is cut
+// into rounds only when every round still fills the GPU.
+long long concurrent_chains(long long chains, bool write_heavy) {
+    const long long forced_grid = env_int("QSSM_GRID", 0);
+    if (forced_grid > 0) return forced_grid < chains ? forced_grid : chains;
+    const double target = write_heavy ? 3.5 * sm_count() : 4.0 * sm_count();
+    long long rounds = (long long)((double)chains / target + (write_heavy ? 0.2 : 0.3));
+    if (rounds < 1) rounds = 1;
+    return (chains + rounds - 1) / rounds;
+}
 
 // Channels per lane.  Two channels per lane halve the shared-memory and copy-engine instructions
 // per element, so one warp moves twice the bytes; narrow strips (V = 1) are for channel counts
@@ -1036,30 +1115,29 @@ size_t ws_bytes_for(long long B, long long D, int n_seg) {
     return (size_t)3 * (size_t)B * (size_t)n_seg * (size_t)D * sizeof(float);
 }
 
-// Ring depth.  All chains of a launch should be resident at once: a chain runs for the whole
-// kernel, so chains that do not fit start only when others finish, and that second wave runs with
-// too few warps to keep HBM busy.  Among the depths lo..hi pick the one that wastes the fewest
-// CTA slots over all waves, preferring deeper rings on a tie.
-int pick_stages(long long chains_total, int stage_bytes, int fixed_bytes, int lo, int hi) {
+// Ring depth.  Measured on B200: these kernels move the most bytes per second when roughly 15 MB of
+// loads and stores are outstanding over the whole GPU (about 28 KB per chain at 512 chains); with
+// more in flight throughput falls again (a fourth backward stage costs 19 %).  So the ring is as
+// deep as that budget allows, within the shared memory an SM can give each of its resident CTAs.
+//   grid          CTAs of the launch (all resident at once)
+//   stage_bytes   one input stage
+//   store_bytes   bytes of stores that can be pending while the ring is full
+//   fixed_bytes   shared memory besides the input stages
+//   prefetch(ns)  input tiles in flight with ns stages
+template <typename F>
+int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_bytes, int lo, int hi, F prefetch) {
     const int forced = env_int("QSSM_STAGES", 0);
     if (forced >= lo && forced <= MAX_STAGES) return forced;
     const long long sms = sm_count();
+    const long long per_sm = (grid + sms - 1) / sms;
+    const long long smem_cap = (228 * 1024) / (per_sm < 1 ? 1 : per_sm) - 1024;
+    const long long budget = (15ll << 20) / (grid < 1 ? 1 : grid);
     int best = lo;
-    double best_eff = -1.0;
     for (int ns = lo; ns <= hi; ++ns) {
-        const long long smem = (long long)ns * stage_bytes + fixed_bytes + MAX_STAGES * 8 + 1024;  // + per-CTA reserve
-        long long per_sm = (227 * 1024 + 1024) / smem;
-        if (per_sm < 1) continue;
-        if (per_sm > 32) per_sm = 32;
-        const long long slots = per_sm * sms;
-        const long long waves = (chains_total + slots - 1) / slots;
-        const double eff = (double)chains_total / (double)(waves * slots);
-        // a single wave is all that matters; beyond that compare slot efficiency
-        const double score = waves == 1 ? 1.0 : eff;
-        if (score >= best_eff) {
-            best_eff = score;
-            best = ns;
-        }
+        const long long smem = (long long)ns * stage_bytes + fixed_bytes + MAX_STAGES * 8;
+        if (smem > smem_cap || smem > 227 * 1024) break;
+        if ((long long)prefetch(ns) * stage_bytes + store_bytes > budget) break;
+        best = ns;
     }
     return best;
 }
@@ -1079,9 +1157,11 @@ int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* s
     g.seg_rows = (int)seg_rows;
     g.status = status;
     g.use_tma = 1;
+    g.l2_hint = env_int("QSSM_L2HINT", 0);
     g.n_stages = 2;
     pl.chains = B * n_seg * g.n_dtiles;
-    if (pl.chains > 0x7fffffffll) return QSSM_E_SHAPE;
+    g.n_chains = pl.chains;
+    pl.grid = concurrent_chains(pl.chains, false);
     return 0;
 }
 
@@ -1157,15 +1237,15 @@ int run_aggregate(bool reverse, const void* t0, const void* t1, const void* t2, 
     ap.A = A;
     ap.H = H;
     const int stage = TB * chans * (2 * dtype_size(in_dtype) + dtype_size(dt2));
-    ap.g.n_stages = pick_stages(pl.chains, stage, 0, 2, 4);
+    ap.g.n_stages = pick_stages(pl.grid, stage, 0, 0, 2, 8, [](int ns) { return ns - 1; });
     const int smem = ap.g.n_stages * stage + MAX_STAGES * 8;
     const int out_dt = reverse ? dt2 : in_dtype;
     return dispatch(in_dtype, out_dt, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
         using Tin = decltype(tin);
         using Tout = decltype(tout);
         constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
-        if (reverse) return launch(scan_agg_kernel<Tin, Tout, V, TBc, true>, ap, pl.chains, smem, stream);
-        return launch(scan_agg_kernel<Tin, Tin, V, TBc, false>, ap, pl.chains, smem, stream);
+        if (reverse) return launch(scan_agg_kernel<Tin, Tout, V, TBc, true>, ap, pl.grid, smem, stream);
+        return launch(scan_agg_kernel<Tin, Tin, V, TBc, false>, ap, pl.grid, smem, stream);
     });
 }
 
@@ -1314,18 +1394,23 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     const int nin = c != nullptr ? 4 : 3;
     const int stage = nin * TB * chans * es;
     const int outbuf = TB * chans * eo + (h_saved != nullptr ? TB * chans * 4 : 0);
-    fp.g.n_stages = pick_stages(pl.chains, stage, 2 * outbuf, 2, 4);
-    const int smem = fp.g.n_stages * stage + 2 * outbuf + MAX_STAGES * 8;
+    int n_out = env_int("QSSM_NOUT", 3);
+    if (n_out < 2) n_out = 2;
+    if (n_out > 4) n_out = 4;
+    fp.g.n_out = n_out;
+    fp.g.n_stages = pick_stages(pl.grid, stage, (n_out - 1) * outbuf, n_out * outbuf, 2, 8,
+                                [](int ns) { return ns - 1; });
+    const int smem = fp.g.n_stages * stage + n_out * outbuf + MAX_STAGES * 8;
     const bool has_c = c != nullptr, save_h = h_saved != nullptr;
 
     return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
         using Tin = decltype(tin);
         using Tout = decltype(tout);
         constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
-        if (has_c && save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, true>, fp, pl.chains, smem, stream);
-        if (has_c) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, false>, fp, pl.chains, smem, stream);
-        if (save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, true>, fp, pl.chains, smem, stream);
-        return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, false>, fp, pl.chains, smem, stream);
+        if (has_c && save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, true>, fp, pl.grid, smem, stream);
+        if (has_c) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, true, false>, fp, pl.grid, smem, stream);
+        if (save_h) return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, true>, fp, pl.grid, smem, stream);
+        return launch(scan_fwd_kernel<Tin, Tout, V, TBc, false, false>, fp, pl.grid, smem, stream);
     });
 }
 
@@ -1427,14 +1512,17 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     const int hrow = chans * 4;
     const int h_tile = saved ? (TB + 1) * hrow : (TB / TS) * hrow;
     const int stage = 4 * TB * chans * es + TB * chans * eo + ((h_tile + 127) / 128) * 128;
-    bp.g.n_stages = pick_stages(pl.chains, stage, 0, 2, 3);
+    pl.grid = concurrent_chains(pl.chains, true);
+    // gradients are stored from the stages themselves: up to two tiles of them pending (one with two stages)
+    bp.g.n_stages = pick_stages(pl.grid, stage, 2 * 4 * TB * chans * es, 0, 2, 6,
+                                [](int ns) { return ns > 2 ? ns - 2 : 1; });
     const int smem = bp.g.n_stages * stage + MAX_STAGES * 8;
     return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
         using Tin = decltype(tin);
         using Tout = decltype(tout);
         constexpr int V = decltype(v)::value, TBc = decltype(tb)::value;
-        if (saved) return launch(scan_bwd_kernel<Tin, Tout, V, TBc, true>, bp, pl.chains, smem, stream);
-        return launch(scan_bwd_kernel<Tin, Tout, V, TBc, false>, bp, pl.chains, smem, stream);
+        if (saved) return launch(scan_bwd_kernel<Tin, Tout, V, TBc, true>, bp, pl.grid, smem, stream);
+        return launch(scan_bwd_kernel<Tin, Tout, V, TBc, false>, bp, pl.grid, smem, stream);
     });
 }
 
