@@ -10,6 +10,9 @@ Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
   cfg2       B=1  L=2^20  D=2048 fp16, decay close to one  (long sequence; --shard seq)
   cfg3_scan  B=16 L=4096  D=4096 bf16 gates, fp32 y / dy   (the scan inside a 12-layer SSM stack)
   cfg4       B=64 L=4096  D=8192 fp16                     (throughput sweep; --shard batch)
+  cfg3_stack 12 x layers.SSM (hidden 1024, state 4096, fp32 parameters, bf16 gates), B=16, L=4096,
+             MSE loss to a random target: whole forward+backward step, with the time spent inside
+             the scan kernels taken separately from CUDA events around every scan call
 With --shard the TOTAL problem is fixed and split over the ranks (strong scaling); the reported
 throughput is total elements over the slowest rank's device time.  One JSON line per run.
 """
@@ -43,15 +46,87 @@ def _median_ms(fn, steps, warmup, sync):
     return statistics.median(out)
 
 
+def run_stack(args):
+    """Configuration 3: the scan inside a 12-layer SSM stack (projections stay torch GEMMs)."""
+    from . import scan_interface
+    from .layers import SSM
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    layers, hidden, B, L = 12, 1024, 16, 4096
+    stack = torch.nn.ModuleList([SSM(hidden_size=hidden, state_size_mult=4.0, dtype=torch.float32,
+                                     compute_dtype=torch.bfloat16, device=dev) for _ in range(layers)])
+    x = torch.randn(B, L, hidden, device=dev)
+    target = torch.randn(B, L, hidden, device=dev)
+
+    # CUDA events around every scan forward and backward
+    events = []
+    fn = scan_interface._TritonScanFunction
+    orig_fwd, orig_bwd = fn.forward, fn.backward
+
+    def timed(orig, kind):
+        def wrapper(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = orig(*a, **k)
+            e1.record()
+            events.append((kind, e0, e1))
+            return out
+        return staticmethod(wrapper)
+
+    fn.forward, fn.backward = timed(orig_fwd, "fwd"), timed(orig_bwd, "bwd")
+    try:
+        def step():
+            h = x
+            for layer in stack:
+                h = layer(h, block_l=256, checkpoint=True)
+            loss = torch.nn.functional.mse_loss(h, target)
+            loss.backward()
+            return loss
+
+        for _ in range(args.warmup):
+            step()
+            stack.zero_grad(set_to_none=True)
+        torch.cuda.synchronize()
+        events.clear()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            loss = step()
+            stack.zero_grad(set_to_none=True)
+        e1.record()
+        torch.cuda.synchronize()
+    finally:
+        fn.forward, fn.backward = orig_fwd, orig_bwd
+    _lib.check_device_status(dev)
+    step_ms = e0.elapsed_time(e1) / args.steps
+    scan_fwd_ms = sum(a.elapsed_time(b) for k, a, b in events if k == "fwd") / args.steps
+    scan_bwd_ms = sum(a.elapsed_time(b) for k, a, b in events if k == "bwd") / args.steps
+    n = B * L * 4096
+    print(json.dumps({
+        "config": "cfg3_stack", "layers": layers, "hidden": hidden, "state_dim": 4096, "B": B, "L": L,
+        "compute_dtype": "bfloat16", "scan_out_dtype": "float32", "loss": float(loss.detach()),
+        "step_ms": round(step_ms, 3), "scan_fwd_ms_per_step": round(scan_fwd_ms, 3),
+        "scan_bwd_ms_per_step": round(scan_bwd_ms, 3),
+        "scan_share_of_step": round((scan_fwd_ms + scan_bwd_ms) / step_ms, 4),
+        "scan_gelems_fwd_bwd": layers * n / ((scan_fwd_ms + scan_bwd_ms) * 1e-3) / 1e9,
+        "scan_calls_per_step": len(events) // args.steps,
+        "note": "scan times include the autograd wrapper (output allocation, dtype casts), 12 layers per step",
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack"])
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--segments", type=int, default=0, help="time segments per GPU (0 = automatic)")
     args = ap.parse_args()
+    if args.config == "cfg3_stack":
+        return run_stack(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
