@@ -49,9 +49,9 @@ extern "C" {
 #define QSSM_E_DRIVER (-7)    /* the CUDA driver entry point for tensor maps is unavailable */
 #define QSSM_E_STATIC_WS (-8) /* qssm_scan_fwd_static_ws: scratch needed exceeds QSSM_STATIC_WS_BYTES */
 
-/* device-side status codes written to *status_word */
+/* device-side status codes written to *status_word (kept apart from cudaError_t values) */
 #define QSSM_S_OK 0
-#define QSSM_S_TMA_TIMEOUT 1  /* a bounded wait on a bulk-copy barrier expired */
+#define QSSM_S_TMA_TIMEOUT 10001  /* a bounded wait on a bulk-copy barrier expired */
 
 /* Rows of time covered by one entry of the `tile_h` boundary-state array. */
 #define QSSM_TILE_ROWS 16

@@ -103,3 +103,26 @@ def test_sequence_sharded_scan_over_nccl(tmp_path, dtype):
     check(got["y"], y_ref, "y")
     for k, ref in zip(("dx", "da", "db", "dc"), g_ref):
         check(got[k], ref, k)
+
+
+def test_streaming_chunks_equal_one_scan():
+    """Pieces of a sequence fed one after the other with the carried state reproduce the whole scan;
+    includes single-step pieces (token-by-token decoding) and an empty piece."""
+    from quick_ssm_b200 import scan
+    from quick_ssm_b200.streaming import ScanState, scan_chunk
+    for dtype in (torch.float32, torch.bfloat16):
+        inp = make_inputs(3, 301, 72, dtype=dtype, seed=17).to("cuda")
+        whole = scan(*inp.tensors())
+        state, outs, pos = None, [], 0
+        for piece in (1, 1, 30, 0, 16, 17, 200, 36):
+            sl = slice(pos, pos + piece)
+            y, state = scan_chunk(inp.x[:, sl], inp.a[:, sl], inp.b[:, sl], inp.c[:, sl], state)
+            outs.append(y)
+            pos += piece
+        assert pos == 301
+        got = torch.cat(outs, dim=1)
+        tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-3)
+        assert torch.allclose(got.float(), whole.float(), **tol)
+        h_all, _ = scan_chunk(inp.x, inp.a, inp.b, None, ScanState.zeros(3, 72))
+        assert torch.allclose(state.h, h_all[:, -1].float(), rtol=2e-2 if dtype != torch.float32 else 1e-5, atol=1e-3)
+    _lib.check_device_status(synchronize=True)

@@ -88,7 +88,7 @@ def test_status_word_raises_once_and_clears():
     w = torch.zeros(1, dtype=torch.int32)
     _lib._status_words[99] = w
     try:
-        w[0] = 1
+        w[0] = 10001
         with pytest.raises(RuntimeError, match="expired"):
             _lib.check_device_status()
         assert int(w[0]) == 0
