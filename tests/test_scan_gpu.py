@@ -73,7 +73,8 @@ def test_fp32_matches_float64_loop(shape, checkpoint, segments):
     _check(got, ref, torch.float32)
 
 
-@pytest.mark.parametrize("shape", [(2, 512, 8), (1, 50, 2), (3, 100, 72), (2, 333, 130), (2, 128, 256)],
+@pytest.mark.parametrize("shape", [(2, 512, 8), (1, 50, 2), (3, 100, 72), (2, 333, 130), (2, 128, 256),
+                                   (2, 100, 330), (1, 45, 520), (3, 17, 1024)],
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
