@@ -201,6 +201,11 @@ __device__ __forceinline__ void tma_st(const CUtensorMap* map, uint32_t src, int
     else
         tma_store_3d(map, src, c0, c1, c2);
 }
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void tma_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
@@ -239,6 +244,20 @@ struct FwdParams {
     Geom g;
 };
 
+// Chained (single-pass) forward for launches with few chains: see scan_fwd_chained_kernel.
+struct ChainedParams {
+    FwdParams f;
+    unsigned int* ticket;   // work counter, zero at launch
+    float* desc;            // [n_chains][slots][3][32] float4 {tag, v0, v1, -}: aggregate A, aggregate H,
+                            // inclusive end state; tag = chunk + 1, the whole area zero at launch
+    int chunk_rows;         // rows per chunk, a multiple of TS
+    int slots;              // descriptor slots per chain (power of two)
+    int n_chunks;           // chunks per chain
+};
+
+struct BwdParams;
+struct ChainedBwdParams;
+
 struct BwdParams {
     TensorDesc x, a, b, c, dy, hsrc;  // hsrc: tile_h (recompute) or h_saved
     TensorDesc dx, da, db, dc;
@@ -246,6 +265,14 @@ struct BwdParams {
     const float* g_in;   // [B, n_seg, D] or NULL
     float* g_first;      // [B, D] or NULL
     Geom g;
+};
+
+// Chained (single-pass) backward: see scan_bwd_chained_kernel.
+struct ChainedBwdParams {
+    BwdParams f;
+    unsigned int* ticket;
+    float* desc;
+    int chunk_rows, slots, n_chunks;
 };
 
 struct AggParams {
@@ -545,6 +572,284 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
 }
 
 // ---------------------------------------------------------------------------------------------
+// Look-back over the chunk descriptors of one chain (chained kernels).
+//
+// Descriptor of chunk j (slot j mod slots): three arrays of 32 float4, one word per lane,
+//   [0..31] {tag, A0, A1, -}   [32..63] {tag, H0, H1, -}   [64..95] {tag, e0, e1, -}
+// with tag = j + 1 (zero = nothing yet); (A, H) is the chunk aggregate, e its inclusive end state.
+// A 16-byte word is written and read with one access, so a word whose tag matches carries its
+// values and no separate flag or fence is needed.
+//
+// Returns in `h` the state entering chunk k: the inclusive end state of the nearest predecessor
+// that has one, pushed through the aggregates of the chunks between it and k ONE BY ONE in time
+// order, h = fma(A_m, h, H_m) - the same expression each of those chunks evaluates for its own
+// end state.  The result is therefore bit-identical whichever predecessors happened to be
+// finished when the warp looked: the kernels stay deterministic although chunks run concurrently.
+// Waits are bounded (about two seconds); false means a predecessor never published.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots, long long k, int lane,
+                                                 float (&h)[2]) {
+    constexpr int WIN = 8;
+    bool ok = true;
+    long long js = -1;  // nearest predecessor whose inclusive end state is known
+    for (long long top = k - 1; js < 0 && ok; top -= WIN) {
+        float4 wi[WIN], wa[WIN], wh[WIN];
+#pragma unroll
+        for (int q = 0; q < WIN; ++q) {
+            const long long j = top - q;
+            if (j >= 0) {
+                const float4* dj = cdesc + (size_t)(j & (slots - 1)) * 96;
+                wi[q] = __ldcg(dj + 64 + lane);
+                wa[q] = __ldcg(dj + lane);
+                wh[q] = __ldcg(dj + 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < WIN; ++q) {
+            const long long j = top - q;
+            if (j < 0 || js >= 0 || !ok) continue;
+            const unsigned int want = (unsigned int)(j + 1);
+            const float4* dj = cdesc + (size_t)(j & (slots - 1)) * 96;
+            bool inc = __all_sync(0xffffffffu, __float_as_uint(wi[q].x) == want);
+            bool agg = __all_sync(0xffffffffu, __float_as_uint(wa[q].x) == want && __float_as_uint(wh[q].x) == want);
+            if (!inc && !agg) {  // nothing published yet: poll this chunk
+                const unsigned long long start = global_timer_ns();
+                for (unsigned int it = 0; ok; ++it) {
+                    wi[q] = __ldcg(dj + 64 + lane);
+                    wa[q] = __ldcg(dj + lane);
+                    wh[q] = __ldcg(dj + 32 + lane);
+                    inc = __all_sync(0xffffffffu, __float_as_uint(wi[q].x) == want);
+                    agg = __all_sync(0xffffffffu,
+                                     __float_as_uint(wa[q].x) == want && __float_as_uint(wh[q].x) == want);
+                    if (inc || agg) break;
+                    __nanosleep(100);
+                    if ((it & 255u) == 255u) {
+                        const bool late = global_timer_ns() - start > 2000000000ull;
+                        if (__any_sync(0xffffffffu, late)) ok = false;
+                    }
+                }
+            }
+            if (ok && inc) {
+                h[0] = wi[q].y;
+                h[1] = wi[q].z;
+                js = j;
+            }
+        }
+    }
+    if (!ok) return false;
+    // forward through the aggregates of chunks js+1 .. k-1 (all seen published above)
+    for (long long base = js + 1; base < k; base += WIN) {
+        float4 wa[WIN], wh[WIN];
+#pragma unroll
+        for (int q = 0; q < WIN; ++q) {
+            const long long j = base + q;
+            if (j < k) {
+                const float4* dj = cdesc + (size_t)(j & (slots - 1)) * 96;
+                wa[q] = __ldcg(dj + lane);
+                wh[q] = __ldcg(dj + 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < WIN; ++q) {
+            if (base + q < k) {
+                h[0] = fmaf(wa[q].y, h[0], wh[q].y);
+                h[1] = fmaf(wa[q].z, h[1], wh[q].z);
+            }
+        }
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// chained forward: one pass over HBM when batch x channels gives too few chains to fill the GPU.
+//
+// Each chain (full time range of one strip) is cut into chunks of `chunk_rows` rows.  Warps take
+// chunks from a global ticket counter in time-major order (chunk k of every chain before chunk
+// k+1 of any), so many chunks of the same chain are in progress at once.  Per chunk a warp
+//   1. streams x, a, b and reduces them to the chunk aggregate (A, H) = (prod a, end state from 0),
+//   2. publishes the aggregate, looks back over the preceding chunks' descriptors - folding
+//      aggregates until it meets a chunk whose inclusive end state is known - to get its h_in,
+//      and publishes its own inclusive end state A*h_in + H,
+//   3. streams the chunk a second time (x, a, b now come from L2, where step 1 left them; only c
+//      comes from HBM) and writes y.
+// HBM traffic is therefore the minimum (each tensor once) as long as the chunks in flight fit L2.
+// Forward progress: a warp waits only on chunks with smaller tickets, all of which are held by
+// warps that are already running; every wait is bounded and a failure makes all warps leave.
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, bool HAS_C>
+__global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_constant__ ChainedParams cp) {
+    constexpr int V = 2;
+    constexpr int DT = 32 * V;
+    constexpr int TB = TS;
+    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
+    constexpr int OUT_ROW = 32 * V * (int)sizeof(Tout);
+    constexpr int IN_TILE = TB * IN_ROW;
+    constexpr int OUT_TILE = TB * OUT_ROW;
+    constexpr int STAGE = 4 * IN_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const FwdParams& p = cp.f;
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    const int NOUT = g.n_out;
+    unsigned char* const outbuf = smem + NS * STAGE;
+    const uint32_t bars = smem_u32(outbuf + NOUT * OUT_TILE);
+    const uint32_t smem_base = smem_u32(smem);
+    const int lane = threadIdx.x;
+    const uint64_t pol_keep = l2_policy_evict_last();
+    const uint64_t pol_drop = l2_policy_evict_first();
+    const bool hint = g.l2_hint != 0;
+
+    if (lane == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
+        fence_barrier_init();
+    }
+    __syncwarp();
+
+    const long long n_chains = g.B * g.n_dtiles;
+    const unsigned int total = (unsigned int)(n_chains * cp.n_chunks);
+    const long long tiles_per_b = (g.L + TS - 1) / TS;
+    RingPos pf{0, 0}, cur{0, 0};
+    int oslot = 0;
+    bool ok = true;
+
+    while (ok) {
+        unsigned int t = 0;
+        if (lane == 0) t = atomicAdd(cp.ticket, 1u);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= total) break;
+        const long long k = t / n_chains;        // chunk index in time
+        const long long c = t % n_chains;        // chain
+        const long long b = c / g.n_dtiles;
+        const long long d0 = (c % g.n_dtiles) * DT;
+        const long long d_lane = d0 + (long long)lane * V;
+        const long long t_begin = k * cp.chunk_rows;
+        long long t_end = t_begin + cp.chunk_rows;
+        if (t_end > g.L) t_end = g.L;
+        const int n_tiles = (int)((t_end - t_begin + TB - 1) / TB);
+        const int c0 = (int)d0, c2 = (int)b;
+
+        // the tile stream of this chunk: n_tiles tiles of pass 1 (x, a, b), then n_tiles of pass 2 (x, a, b, c)
+        int pf_item = 0;
+        const int n_items = 2 * n_tiles;
+        auto issue = [&]() {  // lane 0 only
+            const bool second = pf_item >= n_tiles;
+            const int row = (int)(t_begin + (long long)(second ? pf_item - n_tiles : pf_item) * TB);
+            const uint32_t st = smem_base + pf.s * STAGE;
+            const uint32_t bar = bars + 8 * pf.s;
+            const uint64_t pol = second ? pol_drop : pol_keep;
+            fence_proxy_async();
+            mbar_expect_tx(bar, (second && HAS_C) ? 4 * IN_TILE : 3 * IN_TILE);
+            tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, row, c2, hint, pol);
+            tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, row, c2, hint, pol);
+            tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, row, c2, hint, pol);
+            if (second && HAS_C) tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, row, c2, hint, pol_drop);
+            pf.advance(NS);
+            ++pf_item;
+        };
+        if (lane == 0) {
+            for (int q = 0; q < NS - 1 && pf_item < n_items; ++q) issue();
+        }
+
+        // ---- pass 1: chunk aggregate ----
+        float A[V], H[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) { A[i] = 1.f; H[i] = 0.f; }
+        long long t0 = t_begin;
+        for (int j = 0; j < n_tiles && ok; ++j, t0 += TB) {
+            const unsigned char* st = smem + cur.s * STAGE;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (lane == 0 && pf_item < n_items) issue();
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+#pragma unroll
+            for (int r = 0; r < TB; ++r) {
+                float xv[V], av[V], bv[V];
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 0 * IN_TILE, r, lane), xv);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 1 * IN_TILE, r, lane), av);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 2 * IN_TILE, r, lane), bv);
+                if (r < nrows) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) { A[i] *= av[i]; H[i] = fmaf(av[i], H[i], bv[i] * xv[i]); }
+                }
+            }
+            __syncwarp();
+            cur.advance(NS);
+        }
+        if (!ok) break;
+
+        // ---- carry: publish aggregate, look back, publish inclusive end state ----
+        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
+        float4* const mydesc = cdesc + (size_t)(k & (cp.slots - 1)) * 96;
+        const float mytag = __uint_as_float((unsigned int)(k + 1));
+        float h[V];
+        if (k == 0) {
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                h[i] = (p.h_in != nullptr && d_lane + i < g.D) ? p.h_in[b * g.D + d_lane + i] : 0.f;
+        } else {
+            __stcg(mydesc + lane, make_float4(mytag, A[0], A[1], 0.f));
+            __stcg(mydesc + 32 + lane, make_float4(mytag, H[0], H[1], 0.f));
+            ok = chained_lookback(cdesc, cp.slots, k, lane, h);
+            if (!ok) break;
+        }
+        {   // inclusive end state of this chunk
+            const float e0 = fmaf(A[0], h[0], H[0]), e1 = fmaf(A[1], h[1], H[1]);
+            __stcg(mydesc + 64 + lane, make_float4(mytag, e0, e1, 0.f));
+            if (p.h_last != nullptr && k == cp.n_chunks - 1) {
+                if (d_lane < g.D) p.h_last[b * g.D + d_lane] = e0;
+                if (d_lane + 1 < g.D) p.h_last[b * g.D + d_lane + 1] = e1;
+            }
+        }
+
+        // ---- pass 2: the scan proper, seeded ----
+        float* th_dst = nullptr;
+        if (p.tile_h != nullptr) th_dst = p.tile_h + (b * tiles_per_b + t_begin / TS) * g.D + d_lane;
+        t0 = t_begin;
+        for (int j = 0; j < n_tiles; ++j, t0 += TB) {
+            const unsigned char* st = smem + cur.s * STAGE;
+            unsigned char* ob = outbuf + oslot * OUT_TILE;
+            if (++oslot == NOUT) oslot = 0;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (lane == 0) {
+                if (pf_item < n_items) issue();
+                if (NOUT == 2) tma_wait_read<1>();
+                else if (NOUT == 3) tma_wait_read<2>();
+                else tma_wait_read<3>();
+            }
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (th_dst != nullptr) {
+#pragma unroll
+                for (int i = 0; i < V; ++i)
+                    if (d_lane + i < g.D) th_dst[i] = h[i];
+                th_dst += g.D;
+            }
+            if (nrows >= TS)
+                fwd_batch<Tin, Tout, V, HAS_C, false, true>(st, st + IN_TILE, st + 2 * IN_TILE, st + 3 * IN_TILE, ob,
+                                                            ob, lane, TS, h);
+            else
+                fwd_batch<Tin, Tout, V, HAS_C, false, false>(st, st + IN_TILE, st + 2 * IN_TILE, st + 3 * IN_TILE, ob,
+                                                             ob, lane, nrows, h);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_st(&p.y.map, smem_u32(ob), c0, (int)t0, c2, hint, pol_drop);
+                tma_commit();
+            }
+            __syncwarp();
+            cur.advance(NS);
+        }
+    }
+    if (lane == 0) {
+        tma_wait_all();
+        if (!ok) report(g.status, QSSM_S_TMA_TIMEOUT);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // backward: reverse scan of dh with h rebuilt per 16-row batch (tile_h) or read (h_saved).
 // The carry between batches is G(t) = a(t) * dh(t), so no halo row of `a` is needed.
 // Gradients overwrite the shared-memory slots of x, a, b, c and are stored from there.
@@ -802,6 +1107,199 @@ __global__ void __launch_bounds__(32) scan_bwd_kernel(const __grid_constant__ Bw
 
     if (tma && lane == 0) tma_wait_all();
     if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------
+// chained backward: the reverse-time twin of scan_fwd_chained_kernel.  Chunks are claimed from the
+// last one to the first; per chunk: (1) a, c, dy -> aggregate (P, Q) = (prod a, a(t0) dh(t0) from a
+// zero carry), (2) publish, look back over the chunks later in time, publish the inclusive carry,
+// (3) second pass (a, c, dy now from L2; x, b, tile_h from HBM) with the real carry, gradients
+// stored from the stage as in scan_bwd_kernel.  h is rebuilt from tile_h (checkpoint=True only).
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, typename Tdy>
+__global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_constant__ ChainedBwdParams cp) {
+    constexpr int V = 2;
+    constexpr int DT = 32 * V;
+    constexpr int TB = TS;
+    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
+    constexpr int DY_ROW = 32 * V * (int)sizeof(Tdy);
+    constexpr int H_ROW = 32 * V * 4;
+    constexpr int IN_TILE = TB * IN_ROW;
+    constexpr int DY_TILE = TB * DY_ROW;
+    constexpr int H_SLOT = ((H_ROW + 127) / 128) * 128;
+    constexpr int STAGE = 4 * IN_TILE + DY_TILE + H_SLOT;
+    constexpr int OFF_DY = 4 * IN_TILE;
+    constexpr int OFF_H = OFF_DY + DY_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const BwdParams& p = cp.f;
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    const uint32_t bars = smem_u32(smem + NS * STAGE);
+    const uint32_t smem_base = smem_u32(smem);
+    const int lane = threadIdx.x;
+    const uint64_t pol_keep = l2_policy_evict_last();
+    const uint64_t pol_drop = l2_policy_evict_first();
+    const bool hint = g.l2_hint != 0;
+
+    if (lane == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
+        fence_barrier_init();
+    }
+    __syncwarp();
+
+    const long long n_chains = g.B * g.n_dtiles;
+    const unsigned int total = (unsigned int)(n_chains * cp.n_chunks);
+    RingPos pf{0, 0}, cur{0, 0};
+    const int PF = NS > 2 ? NS - 2 : 1;
+    bool ok = true;
+
+    while (ok) {
+        unsigned int t = 0;
+        if (lane == 0) t = atomicAdd(cp.ticket, 1u);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t >= total) break;
+        const long long kk = t / n_chains;             // position in processing order
+        const long long k = cp.n_chunks - 1 - kk;      // chunk index in time
+        const long long c = t % n_chains;
+        const long long b = c / g.n_dtiles;
+        const long long d0 = (c % g.n_dtiles) * DT;
+        const long long d_lane = d0 + (long long)lane * V;
+        const long long t_begin = k * cp.chunk_rows;
+        long long t_end = t_begin + cp.chunk_rows;
+        if (t_end > g.L) t_end = g.L;
+        const int n_tiles = (int)((t_end - t_begin + TB - 1) / TB);
+        const int c0 = (int)d0, c2 = (int)b;
+
+        int pf_item = 0;
+        const int n_items = 2 * n_tiles;
+        auto issue = [&]() {  // lane 0 only; tiles of a pass run from the end of the chunk to its start
+            const bool second = pf_item >= n_tiles;
+            const int idx = second ? pf_item - n_tiles : pf_item;
+            const int row = (int)(t_begin + (long long)(n_tiles - 1 - idx) * TB);
+            const uint32_t st = smem_base + pf.s * STAGE;
+            const uint32_t bar = bars + 8 * pf.s;
+            fence_proxy_async();
+            if (!second) {
+                mbar_expect_tx(bar, 2 * IN_TILE + DY_TILE);
+                tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, row, c2, hint, pol_keep);
+                tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, row, c2, hint, pol_keep);
+                tma_ld(st + OFF_DY, &p.dy.map, bar, c0, row, c2, hint, pol_keep);
+            } else {
+                mbar_expect_tx(bar, 4 * IN_TILE + DY_TILE + H_ROW);
+                tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, row, c2, hint, pol_drop);
+                tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, row, c2, hint, pol_drop);
+                tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, row, c2, hint, pol_drop);
+                tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, row, c2, hint, pol_drop);
+                tma_ld(st + OFF_DY, &p.dy.map, bar, c0, row, c2, hint, pol_drop);
+                tma_ld(st + OFF_H, &p.hsrc.map, bar, c0, row / TS, c2, hint, pol_drop);
+            }
+            pf.advance(NS);
+            ++pf_item;
+        };
+        // a stage is refilled only when the gradient store issued from it (if any) has drained
+        auto refill = [&]() {
+            if (NS > 2) tma_wait_read<1>();
+            else tma_wait_read<0>();
+            issue();
+        };
+        if (lane == 0) {
+            for (int q = 0; q < PF && pf_item < n_items; ++q) refill();
+        }
+
+        // ---- pass 1: chunk aggregate, rows from the end of the chunk to its start ----
+        float P[V], Q[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) { P[i] = 1.f; Q[i] = 0.f; }
+        long long t0 = t_begin + (long long)(n_tiles - 1) * TB;
+        for (int j = 0; j < n_tiles; ++j, t0 -= TB) {
+            const unsigned char* st = smem + cur.s * STAGE;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (lane == 0 && pf_item < n_items) refill();
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+#pragma unroll
+            for (int r = TB - 1; r >= 0; --r) {
+                float av[V], cv[V], gy[V];
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 1 * IN_TILE, r, lane), av);
+                unpack<Tin, V>(tile_raw<Tin, V>(st + 3 * IN_TILE, r, lane), cv);
+                unpack<Tdy, V>(tile_raw<Tdy, V>(st + OFF_DY, r, lane), gy);
+                if (r < nrows) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) { P[i] *= av[i]; Q[i] = av[i] * fmaf(cv[i], gy[i], Q[i]); }
+                }
+            }
+            __syncwarp();
+            cur.advance(NS);
+        }
+        if (!ok) break;
+
+        // ---- carry: same descriptor protocol as the forward, in processing order kk ----
+        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
+        float4* const mydesc = cdesc + (size_t)(kk & (cp.slots - 1)) * 96;
+        const float mytag = __uint_as_float((unsigned int)(kk + 1));
+        float G[V];
+        if (kk == 0) {
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                G[i] = (p.g_in != nullptr && d_lane + i < g.D) ? p.g_in[b * g.D + d_lane + i] : 0.f;
+        } else {
+            __stcg(mydesc + lane, make_float4(mytag, P[0], P[1], 0.f));
+            __stcg(mydesc + 32 + lane, make_float4(mytag, Q[0], Q[1], 0.f));
+            ok = chained_lookback(cdesc, cp.slots, kk, lane, G);
+            if (!ok) break;
+        }
+        {
+            const float e0 = fmaf(P[0], G[0], Q[0]), e1 = fmaf(P[1], G[1], Q[1]);
+            __stcg(mydesc + 64 + lane, make_float4(mytag, e0, e1, 0.f));
+            if (p.g_first != nullptr && k == 0) {
+                if (d_lane < g.D) p.g_first[b * g.D + d_lane] = e0;
+                if (d_lane + 1 < g.D) p.g_first[b * g.D + d_lane + 1] = e1;
+            }
+        }
+
+        // ---- pass 2: gradients ----
+        t0 = t_begin + (long long)(n_tiles - 1) * TB;
+        for (int j = 0; j < n_tiles; ++j, t0 -= TB) {
+            unsigned char* st = smem + cur.s * STAGE;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (lane == 0 && pf_item < n_items) refill();
+            ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            unsigned char* sx = st;
+            unsigned char* sa = st + IN_TILE;
+            unsigned char* sb = st + 2 * IN_TILE;
+            unsigned char* sc = st + 3 * IN_TILE;
+            if (nrows >= TS)
+                bwd_batch<Tin, Tdy, V, false, true>(sx, sa, sb, sc, st + OFF_DY, st + OFF_H, sx, sa, sb, sc, 0, lane, TS,
+                                                    false, nullptr, d_lane, g.D, G);
+            else
+                bwd_batch<Tin, Tdy, V, false, false>(sx, sa, sb, sc, st + OFF_DY, st + OFF_H, sx, sa, sb, sc, 0, lane,
+                                                     nrows, false, nullptr, d_lane, g.D, G);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t sst = smem_base + cur.s * STAGE;
+                tma_st(&p.dx.map, sst + 0 * IN_TILE, c0, (int)t0, c2, hint, pol_drop);
+                tma_st(&p.da.map, sst + 1 * IN_TILE, c0, (int)t0, c2, hint, pol_drop);
+                tma_st(&p.db.map, sst + 2 * IN_TILE, c0, (int)t0, c2, hint, pol_drop);
+                tma_st(&p.dc.map, sst + 3 * IN_TILE, c0, (int)t0, c2, hint, pol_drop);
+                tma_commit();
+            }
+            __syncwarp();
+            cur.advance(NS);
+        }
+        if (!ok) break;
+        // the stores of this chunk must have read their stages before the next chunk refills them
+        if (lane == 0) tma_wait_read<0>();
+        __syncwarp();
+    }
+    if (lane == 0) {
+        tma_wait_all();
+        if (!ok) report(g.status, QSSM_S_TMA_TIMEOUT);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1464,6 +1962,61 @@ int static_ws_address(void** out) {
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// chained forward: host side
+// ---------------------------------------------------------------------------------------------
+struct ChainedLayout {
+    long long n_chains, grid;
+    int slots, chunk_rows, n_chunks;
+    size_t desc_off, bytes, zero_bytes;
+};
+
+// 0 = never, 1 = when the time axis would otherwise be segmented, 2 = whenever the shape allows (tests)
+int chained_mode() { return env_int("QSSM_CHAINED", 1); }
+
+// Chunks of 256 rows of 16-bit data (128 of fp32): with about a thousand chunks in flight the three
+// tensors the first pass leaves in L2 for the second one take ~100 MB of the 126 MB L2; measured on
+// B200 the second pass then reads them from L2 (DRAM reads = one pass), with 512 rows it does not.
+ChainedLayout chained_layout(long long B, long long L, long long D, int elem_size) {
+    ChainedLayout c;
+    c.n_chains = B * ((D + 63) / 64);
+    c.chunk_rows = env_int("QSSM_CHUNK_ROWS", elem_size == 2 ? 256 : 128);
+    if (c.chunk_rows < TS) c.chunk_rows = TS;
+    c.chunk_rows = (c.chunk_rows / TS) * TS;
+    c.n_chunks = (int)((L + c.chunk_rows - 1) / c.chunk_rows);
+    // two warps per scheduler: the two passes make a lone warp per scheduler compute-bound
+    c.grid = env_int("QSSM_CHAINED_GRID", 0) > 0 ? env_int("QSSM_CHAINED_GRID", 0) : 8ll * sm_count();
+    const long long total = c.n_chains * c.n_chunks;
+    if (c.grid > total) c.grid = total;
+    if (c.grid < 1) c.grid = 1;
+    long long need = (c.grid + c.n_chains - 1) / c.n_chains + 2;  // chunks of one chain in flight, plus slack
+    int slots = 4;
+    while (slots < need) slots <<= 1;
+    c.slots = slots;
+    c.desc_off = 256;
+    c.bytes = c.desc_off + (size_t)c.n_chains * slots * 96 * 16;
+    c.zero_bytes = c.bytes;
+    return c;
+}
+
+bool chained_shape_ok(long long B, long long L, long long D) {
+    return B > 0 && L >= 4 * TS && D > 32 && B * ((D + 63) / 64) * ((L + TS - 1) / TS) < 0x7fffffffll;
+}
+
+size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
+    const int mode = chained_mode();
+    if (mode == 0 || !chained_shape_ok(B, L, D)) return 0;
+    if (mode == 1 && auto_segments(B, L, D, in_dtype) <= 1) return 0;
+    return chained_layout(B, L, D, dtype_size(in_dtype)).bytes;
+}
+
+template <typename K> long long resident_ctas(K kernel, int threads, int smem) {
+    int per_sm = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) return 0;
+    return (long long)per_sm * sm_count();
+}
+
 }  // namespace
 
 // =============================================================================================
@@ -1495,7 +2048,9 @@ const char* qssm_status_string(int code) {
 }
 
 size_t qssm_workspace_bytes(int64_t B, int64_t L, int64_t D, int in_dtype) {
-    return ws_bytes_for(B, D, auto_segments(B, L, D, in_dtype));
+    const size_t seg = ws_bytes_for(B, D, auto_segments(B, L, D, in_dtype));
+    const size_t chained = chained_ws_bytes(B, L, D, in_dtype);
+    return seg > chained ? seg : chained;
 }
 
 int qssm_auto_segments(int64_t B, int64_t L, int64_t D, int in_dtype) { return auto_segments(B, L, D, in_dtype); }
@@ -1519,6 +2074,63 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     if (x == nullptr || a == nullptr || b == nullptr || y == nullptr) return QSSM_E_NULL;
     if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
     if ((rc = check_strides(L, D, out_stride_b, out_stride_l))) return rc;
+
+    // Few chains, long sequence: single-pass chained kernel instead of aggregate + carry + scan.
+    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && env_int("QSSM_NO_TMA", 0) == 0) {
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype);
+        const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+        if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+            tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
+            tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo)) {
+            const ChainedLayout lay = chained_layout(B, L, D, es);
+            ChainedParams cp;
+            memset(&cp, 0, sizeof(cp));
+            Geom& g = cp.f.g;
+            g.B = B; g.L = L; g.D = D;
+            g.n_dtiles = (int)((D + 63) / 64);
+            g.n_seg = 1;
+            g.seg_rows = 0;
+            g.use_tma = 1;
+            g.l2_hint = env_int("QSSM_CHAINED_HINT", 1);
+            g.status = status_word;
+            g.n_chains = lay.n_chains;
+            g.n_out = 3;
+            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0) : 3;
+            const int chans = 64;
+            if ((rc = fill_desc(cp.f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(cp.f.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(cp.f.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(cp.f.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(cp.f.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TS, true))) return rc;
+            cp.f.tile_h = tile_h;
+            cp.f.h_in = h_in;
+            cp.f.h_last = h_last;
+            unsigned char* base = static_cast<unsigned char*>(ws);
+            cp.ticket = reinterpret_cast<unsigned int*>(base);
+            cp.desc = reinterpret_cast<float*>(base + lay.desc_off);
+            cp.chunk_rows = lay.chunk_rows;
+            cp.slots = lay.slots;
+            cp.n_chunks = lay.n_chunks;
+            const int smem = g.n_stages * 4 * TS * chans * es + g.n_out * TS * chans * eo + MAX_STAGES * 8;
+            const bool has_c = c != nullptr;
+            return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
+                using Tin = decltype(tin);
+                using Tout = decltype(tout);
+                auto go = [&](auto kernel) -> int {
+                    // every CTA must be resident: warps wait on chunks held by other running warps
+                    long long grid = lay.grid;
+                    const long long cap = resident_ctas(kernel, 32, smem);
+                    if (cap < 1) return QSSM_E_SHAPE;
+                    if (grid > cap) grid = cap;
+                    cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
+                    if (e != cudaSuccess) return (int)e;
+                    return launch(kernel, cp, grid, smem, stream);
+                };
+                if (has_c) return go(scan_fwd_chained_kernel<Tin, Tout, true>);
+                return go(scan_fwd_chained_kernel<Tin, Tout, false>);
+            });
+        }
+    }
 
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
@@ -1625,6 +2237,67 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     if (h_saved == nullptr && tile_h == nullptr) return QSSM_E_NEED_H;
     if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
     if ((rc = check_strides(L, D, dy_stride_b, dy_stride_l))) return rc;
+
+    // Few chains, long sequence: single-pass chained kernel (h rebuilt from tile_h only).
+    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && env_int("QSSM_NO_TMA", 0) == 0) {
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype);
+        const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+        const long long n_tiles_b = (L + TS - 1) / TS;
+        const long long g_sb = L * D, g_sl = D;
+        if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+            tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
+            tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(dy, B, L, D, dy_stride_b, dy_stride_l, eo) &&
+            tma_ok(dx, B, L, D, g_sb, g_sl, es) && tma_ok(da, B, L, D, g_sb, g_sl, es) &&
+            tma_ok(db, B, L, D, g_sb, g_sl, es) && tma_ok(dc, B, L, D, g_sb, g_sl, es) &&
+            tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4)) {
+            const ChainedLayout lay = chained_layout(B, L, D, es);
+            ChainedBwdParams cp;
+            memset(&cp, 0, sizeof(cp));
+            Geom& g = cp.f.g;
+            g.B = B; g.L = L; g.D = D;
+            g.n_dtiles = (int)((D + 63) / 64);
+            g.n_seg = 1;
+            g.use_tma = 1;
+            g.l2_hint = env_int("QSSM_CHAINED_HINT", 1);
+            g.status = status_word;
+            g.n_chains = lay.n_chains;
+            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0) : 4;
+            const int chans = 64;
+            BwdParams& f = cp.f;
+            if ((rc = fill_desc(f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, 1, true))) return rc;
+            if ((rc = fill_desc(f.dx, dx, in_dtype, B, L, D, g_sb, g_sl, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.da, da, in_dtype, B, L, D, g_sb, g_sl, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.db, db, in_dtype, B, L, D, g_sb, g_sl, chans, TS, true))) return rc;
+            if ((rc = fill_desc(f.dc, dc, in_dtype, B, L, D, g_sb, g_sl, chans, TS, true))) return rc;
+            f.g_in = g_in;
+            f.g_first = g_first;
+            unsigned char* base = static_cast<unsigned char*>(ws);
+            cp.ticket = reinterpret_cast<unsigned int*>(base);
+            cp.desc = reinterpret_cast<float*>(base + lay.desc_off);
+            cp.chunk_rows = lay.chunk_rows;
+            cp.slots = lay.slots;
+            cp.n_chunks = lay.n_chunks;
+            const int stage = 4 * TS * chans * es + TS * chans * eo + ((chans * 4 + 127) / 128) * 128;
+            const int smem = g.n_stages * stage + MAX_STAGES * 8;
+            return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
+                using Tin = decltype(tin);
+                using Tout = decltype(tout);
+                auto kernel = scan_bwd_chained_kernel<Tin, Tout>;
+                long long grid = lay.grid;
+                const long long cap = resident_ctas(kernel, 32, smem);  // every CTA must be resident
+                if (cap < 1) return QSSM_E_SHAPE;
+                if (grid > cap) grid = cap;
+                cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
+                if (e != cudaSuccess) return (int)e;
+                return launch(kernel, cp, grid, smem, stream);
+            });
+        }
+    }
 
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;

@@ -68,7 +68,8 @@ def test_workspace_and_segment_policy():
     # long sequence, few channels: segmented
     n = lib.qssm_auto_segments(1, 1 << 20, 2048, 1)
     assert n > 1
-    assert lib.qssm_workspace_bytes(1, 1 << 20, 2048, 1) == 3 * 1 * n * 2048 * 4
+    # scratch covers both ways of running it: segment aggregates, or the chunk descriptors of the single-pass kernel
+    assert lib.qssm_workspace_bytes(1, 1 << 20, 2048, 1) >= 3 * 1 * n * 2048 * 4
     # short sequences are never cut below 256 rows per segment
     assert lib.qssm_auto_segments(1, 300, 32, 0) == 1
 

@@ -288,3 +288,49 @@ def test_segment_aggregates_are_reused_by_the_scan():
     _lib.check_device_status(synchronize=True)
     for w, h in zip(want, have):
         assert torch.equal(w, h)
+
+
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (1, 5000, 72)), (torch.bfloat16, (2, 3001, 200)),
+                                         (torch.float16, (3, 700, 64))], ids=["fp32", "bf16", "fp16"])
+@pytest.mark.parametrize("chunk_rows", [64, 256])
+def test_chained_single_pass_forward(monkeypatch, dtype, shape, chunk_rows):
+    """The single-pass forward for few chains (chunks claimed from a ticket counter, carries found by
+    looking back over chunk descriptors), forced on small shapes: forward, boundary states (through the
+    backward that consumes them), seed and end state."""
+    monkeypatch.setenv("QSSM_CHAINED", "2")
+    monkeypatch.setenv("QSSM_CHUNK_ROWS", str(chunk_rows))
+    inp = make_inputs(*shape, dtype=dtype, seed=23)
+    ref = _oracle(inp, np.float64 if dtype == torch.float32 else np.float32)
+    got = _run_scan(inp)
+    _check(got, ref, dtype)
+    # seeded, with the end state
+    x, a, b, c = (t.to(DEV) for t in inp.tensors())
+    B, L, D = x.shape
+    h0 = torch.randn(B, D, device=DEV)
+    y = torch.empty_like(x)
+    h_last = torch.empty(B, D, device=DEV)
+    _lib.scan_fwd(x, a, b, c, y, h_in=h0, h_last=h_last)
+    monkeypatch.setenv("QSSM_CHAINED", "0")
+    y_ref = torch.empty_like(x)
+    h_ref = torch.empty(B, D, device=DEV)
+    _lib.scan_fwd(x, a, b, c, y_ref, h_in=h0, h_last=h_ref, n_seg=1)
+    _lib.check_device_status(synchronize=True)
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-3)
+    assert torch.allclose(y.float(), y_ref.float(), **tol)
+    assert torch.allclose(h_last, h_ref, rtol=1e-4, atol=1e-5)
+
+
+def test_chained_single_pass_is_deterministic(monkeypatch):
+    """Chunks run concurrently and find their carries in whatever state the predecessors are in, but the
+    carry is always folded chunk by chunk in time order: results are bit-identical from run to run and
+    for any number of warps working at once."""
+    monkeypatch.setenv("QSSM_CHAINED", "2")
+    monkeypatch.setenv("QSSM_CHUNK_ROWS", "64")
+    inp = make_inputs(2, 20000, 128, dtype=torch.bfloat16, seed=31)
+    runs = []
+    for grid in ("0", "0", "37", "1000"):
+        monkeypatch.setenv("QSSM_CHAINED_GRID", grid)
+        runs.append(_run_scan(inp))
+    for other in runs[1:]:
+        for k in runs[0]:
+            assert torch.equal(runs[0][k], other[k]), k
