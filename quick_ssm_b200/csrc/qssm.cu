@@ -2006,7 +2006,9 @@ bool chained_shape_ok(long long B, long long L, long long D) {
 size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
     const int mode = chained_mode();
     if (mode == 0 || !chained_shape_ok(B, L, D)) return 0;
-    if (mode == 1 && auto_segments(B, L, D, in_dtype) <= 1) return 0;
+    // measured crossover: below about 2.75 chains per SM the chained kernels (~182 Gelem/s fwd+bwd on
+    // 16-bit data whatever the chain count) beat one warp per chain (168 at 384 chains, 196 at 448)
+    if (mode == 1 && 4 * B * ((D + 63) / 64) >= 11 * (long long)sm_count()) return 0;
     return chained_layout(B, L, D, dtype_size(in_dtype)).bytes;
 }
 
