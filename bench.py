@@ -261,8 +261,11 @@ def run_gpu(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     e2e_launches = pipe.kernel_launches - launches0
-    # the host results of the last step must equal the device-resident results
-    same = torch.equal(host["dx"][-1].to(dev), grads[0][-1]) and torch.equal(host["y"][0].to(dev), y[0])
+    # the host results of the last step must agree with the device-resident results (same kernels on
+    # batch slices; a slice may take the chunked single-pass kernels, whose carries round differently)
+    def _close(u, v):
+        return torch.allclose(u.float(), v.float(), rtol=2e-2, atol=1e-3)
+    same = _close(host["dx"][-1].to(dev), grads[0][-1]) and _close(host["y"][0].to(dev), y[0])
     if not same:
         raise SystemExit("e2e host-buffer path disagrees with the device-resident path")
 

@@ -32,18 +32,17 @@ from .synth import CONFIGS, make_inputs
 
 
 def _median_ms(fn, steps, warmup, sync):
-    for _ in range(warmup):
+    """Mean device time of `steps` back-to-back calls (CUDA events on the launching stream)."""
+    for _ in range(max(3, warmup)):
         fn()
     sync()
-    out = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     for _ in range(steps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
         fn()
-        e1.record()
-        torch.cuda.synchronize()
-        out.append(e0.elapsed_time(e1))
-    return statistics.median(out)
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / steps
 
 
 def run_stack(args):
