@@ -22,11 +22,16 @@ def _nvcc() -> str:
     return cand if os.path.exists(cand) else "nvcc"
 
 
+def _sources():
+    csrc = os.path.dirname(SRC)
+    return [os.path.join(csrc, f) for f in sorted(os.listdir(csrc)) if f.endswith((".cu", ".cuh"))] + [HEADER]
+
+
 def is_stale() -> bool:
     if not os.path.exists(LIB):
         return True
     built = os.path.getmtime(LIB)
-    return any(os.path.exists(p) and os.path.getmtime(p) > built for p in (SRC, HEADER))
+    return any(os.path.getmtime(p) > built for p in _sources())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
