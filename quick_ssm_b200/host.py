@@ -34,11 +34,11 @@ class HostScan:
     """Forward + backward scan over pinned host buffers, pipelined over batch slices."""
 
     def __init__(self, B: int, L: int, D: int, dtype: torch.dtype, out_dtype: Optional[torch.dtype] = None,
-                 device="cuda", batch_slice: Optional[int] = None, ring: int = 2):
+                 device="cuda", batch_slice: Optional[int] = None, ring: int = 3):
         self.B, self.L, self.D = B, L, D
         self.dtype, self.out_dtype = dtype, out_dtype or dtype
         self.device = torch.device(device)
-        self.bs = batch_slice or max(1, B // 4)
+        self.bs = batch_slice or max(1, B // 8)
         self.ring = ring
         nt = (L + _lib.tile_rows() - 1) // _lib.tile_rows()
         self.sets = []
@@ -53,6 +53,10 @@ class HostScan:
         self.s_k = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
         self.kernel_launches = 0
+        # last users of every device buffer set, kept across calls so that consecutive calls overlap
+        self._drained = [None] * ring   # D2H of the slice that last used a set
+        self._computed = [None] * ring  # kernels of the slice that last used a set
+        self._next = 0
 
     @property
     def h2d_bytes(self) -> int:
@@ -65,18 +69,19 @@ class HostScan:
         return self.h2d_bytes  # y in out_dtype + four gradients in the input dtype
 
     def run(self, host: Dict[str, torch.Tensor]) -> torch.cuda.Event:
-        """Enqueue one forward+backward over ``host`` (see ``alloc_pinned``); returns the event
-        that marks the last device->host copy."""
+        """Enqueue one forward+backward over ``host`` (see ``alloc_pinned``) and return the event that
+        marks its last device->host copy.  The call does not wait: the caller synchronises on the
+        event (or the device) before reading the results.  The input buffers must stay unchanged
+        until then; consecutive calls overlap their transfers."""
         cur = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_k, self.s_out):
-            s.wait_stream(cur)
-        drained = [None] * self.ring   # D2H of the slice that last used a buffer set
-        computed = [None] * self.ring  # kernels of the slice that last used a buffer set
+        self.s_in.wait_stream(cur)  # whatever produced the host-visible inputs on this stream
+        drained, computed = self._drained, self._computed
         last = None
-        for i, lo in enumerate(range(0, self.B, self.bs)):
+        for lo in range(0, self.B, self.bs):
             hi = min(lo + self.bs, self.B)
             n = hi - lo
-            k = i % self.ring
+            k = self._next
+            self._next = (k + 1) % self.ring
             dev = self.sets[k]
             with torch.cuda.stream(self.s_in):
                 if computed[k] is not None:
@@ -105,5 +110,4 @@ class HostScan:
                 out.record(self.s_out)
                 drained[k] = out
                 last = out
-        cur.wait_stream(self.s_out)
         return last
