@@ -188,7 +188,7 @@ int auto_segments(long long B, long long L, long long D, int in_dtype) {
     const long long chains = B * ((D + 63) / 64);
     const long long sms = sm_count();
     if (chains >= 2 * sms) return 1;
-    long long want = (4 * sms + chains - 1) / chains;
+    long long want = (4 * sms) / chains;  // rounded down: never more chains than four per SM hold at once
     const long long max_by_len = L / 256;  // at least 256 rows per segment
     if (want > max_by_len) want = max_by_len;
     if (want < 2) want = 1;
@@ -767,8 +767,14 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
         rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, TB / TS, tma);
     if (rc) return rc;
     // Four adjacent strips per CTA with one store per gradient tensor (16-bit storage, full-width rows).
-    const bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS &&
-                      pl.g.n_dtiles >= WIDE_W;
+    // One such CTA fits per SM, so the groups must fill whole rounds of SM-count CTAs reasonably well;
+    // otherwise (e.g. 152 groups on 148 SMs) the one-warp-per-CTA kernel, which packs finer, is used.
+    bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W;
+    if (wide) {
+        const long long groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
+        const long long rounds = (groups + sm_count() - 1) / sm_count();
+        if ((double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
+    }
     const int out_box = wide ? WIDE_W * chans : chans;
     if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
     if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
@@ -785,8 +791,8 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     if (wide) {
         const int n_dgroups = (pl.g.n_dtiles + WIDE_W - 1) / WIDE_W;
         const long long n_groups = B * n_seg * n_dgroups;
-        long long ctas = (concurrent_chains(n_groups * WIDE_W, true) + WIDE_W - 1) / WIDE_W;
-        if (ctas > n_groups) ctas = n_groups;
+        const long long wide_rounds = (n_groups + sm_count() - 1) / sm_count();
+        long long ctas = (n_groups + wide_rounds - 1) / wide_rounds;  // equal rounds, at most one CTA per SM
         int n_out = env_int("QSSM_NOUT_BWD", 2);
         if (n_out < 2) n_out = 2;
         if (n_out > 3) n_out = 3;
