@@ -431,6 +431,29 @@ size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
     return chained_layout(B, L, D, dtype_size(in_dtype)).bytes;
 }
 
+unsigned long long lookback_wait_ns() {
+    const int ms = env_int("QSSM_WAIT_MS", 2000);
+    return (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+}
+
+// Zero the ticket counter and the descriptors.  Test hook (QSSM_TEST_SKIP_FIRST_CHUNK=1): start the
+// counter past the first chunk of every chain, so that nothing ever publishes those chunks and every
+// look-back wait runs into its limit - the way to exercise the bounded-wait error path on a healthy GPU.
+int prepare_chained_ws(void* ws, const ChainedLayout& lay, cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
+    if (e != cudaSuccess) return (int)e;
+    if (env_int("QSSM_TEST_SKIP_FIRST_CHUNK", 0) != 0) {
+        static unsigned int start[MAX_DEVICES];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= MAX_DEVICES) return QSSM_E_SHAPE;
+        start[dev] = (unsigned int)lay.n_chains;
+        e = cudaMemcpyAsync(ws, &start[dev], sizeof(unsigned int), cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
 template <typename K> long long resident_ctas(K kernel, int threads, int smem) {
     int per_sm = 0;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
@@ -532,6 +555,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
             cp.chunk_rows = lay.chunk_rows;
             cp.slots = lay.slots;
             cp.n_chunks = lay.n_chunks;
+            cp.wait_ns = lookback_wait_ns();
             const int smem = g.n_stages * 4 * TS * chans * es + g.n_out * TS * chans * eo + MAX_STAGES * 8;
             const bool has_c = c != nullptr;
             return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
@@ -543,8 +567,8 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
                     const long long cap = resident_ctas(kernel, 32, smem);
                     if (cap < 1) return QSSM_E_SHAPE;
                     if (grid > cap) grid = cap;
-                    cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
-                    if (e != cudaSuccess) return (int)e;
+                    const int prc = prepare_chained_ws(ws, lay, stream);
+                    if (prc) return prc;
                     return launch(kernel, cp, grid, smem, stream);
                 };
                 if (has_c) return go(scan_fwd_chained_kernel<Tin, Tout, true>);
@@ -703,6 +727,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
             cp.chunk_rows = lay.chunk_rows;
             cp.slots = lay.slots;
             cp.n_chunks = lay.n_chunks;
+            cp.wait_ns = lookback_wait_ns();
             const int stage = 4 * TS * chans * es + TS * chans * eo + ((chans * 4 + 127) / 128) * 128;
             const int smem = g.n_stages * stage + MAX_STAGES * 8;
             return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
@@ -713,8 +738,8 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
                 const long long cap = resident_ctas(kernel, 32, smem);  // every CTA must be resident
                 if (cap < 1) return QSSM_E_SHAPE;
                 if (grid > cap) grid = cap;
-                cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
-                if (e != cudaSuccess) return (int)e;
+                const int prc = prepare_chained_ws(ws, lay, stream);
+                if (prc) return prc;
                 return launch(kernel, cp, grid, smem, stream);
             });
         }

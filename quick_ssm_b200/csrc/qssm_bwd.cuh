@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
         } else {
             __stcg(mydesc + lane, make_float4(mytag, P[0], P[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, Q[0], Q[1], 0.f));
-            ok = chained_lookback(cdesc, cp.slots, kk, lane, G);
+            ok = chained_lookback(cdesc, cp.slots, kk, lane, cp.wait_ns, G);
             if (!ok) break;
         }
         {

@@ -226,10 +226,10 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
 // order, h = fma(A_m, h, H_m) - the same expression each of those chunks evaluates for its own
 // end state.  The result is therefore bit-identical whichever predecessors happened to be
 // finished when the warp looked: the kernels stay deterministic although chunks run concurrently.
-// Waits are bounded (about two seconds); false means a predecessor never published.
+// Waits are bounded (`wait_ns`, two seconds by default); false means a predecessor never published.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots, long long k, int lane,
-                                                 float (&h)[2]) {
+                                                 unsigned long long wait_ns, float (&h)[2]) {
     constexpr int WIN = 8;
     bool ok = true;
     long long js = -1;  // nearest predecessor whose inclusive end state is known
@@ -265,7 +265,7 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                     if (inc || agg) break;
                     __nanosleep(100);
                     if ((it & 255u) == 255u) {
-                        const bool late = global_timer_ns() - start > 2000000000ull;
+                        const bool late = global_timer_ns() - start > wait_ns;
                         if (__any_sync(0xffffffffu, late)) ok = false;
                     }
                 }
@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_const
         } else {
             __stcg(mydesc + lane, make_float4(mytag, A[0], A[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, H[0], H[1], 0.f));
-            ok = chained_lookback(cdesc, cp.slots, k, lane, h);
+            ok = chained_lookback(cdesc, cp.slots, k, lane, cp.wait_ns, h);
             if (!ok) break;
         }
         {   // inclusive end state of this chunk

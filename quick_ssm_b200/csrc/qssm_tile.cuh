@@ -114,6 +114,7 @@ struct ChainedParams {
     int chunk_rows;         // rows per chunk, a multiple of TS
     int slots;              // descriptor slots per chain (power of two)
     int n_chunks;           // chunks per chain
+    unsigned long long wait_ns;  // limit of a look-back wait
 };
 
 struct BwdParams;
@@ -134,6 +135,7 @@ struct ChainedBwdParams {
     unsigned int* ticket;
     float* desc;
     int chunk_rows, slots, n_chunks;
+    unsigned long long wait_ns;
 };
 
 struct AggParams {

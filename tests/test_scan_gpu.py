@@ -382,3 +382,25 @@ def test_every_kernel_variant_gives_the_same_answer(monkeypatch, env):
         _check(got, ref, torch.bfloat16)
         for k in base:
             assert torch.allclose(got[k].float(), base[k].float(), rtol=2e-2, atol=1e-3), k
+
+
+def test_expired_wait_is_reported_and_the_context_survives(monkeypatch):
+    """The failure path of the bounded waits, on a healthy GPU: a test hook starts the chunk counter of
+    the single-pass kernel past the first chunk of every chain, so nothing ever publishes those chunks;
+    the look-back waits of the other chunks run into their (shortened) limit, the kernel records the
+    status code and returns, the host raises, and the next launch works as usual."""
+    monkeypatch.setenv("QSSM_CHAINED", "2")
+    monkeypatch.setenv("QSSM_CHUNK_ROWS", "64")
+    monkeypatch.setenv("QSSM_WAIT_MS", "100")
+    inp = make_inputs(1, 2000, 64, dtype=torch.float32, seed=51).to(DEV)
+    x, a, b, c = inp.tensors()
+    y = torch.empty_like(x)
+    monkeypatch.setenv("QSSM_TEST_SKIP_FIRST_CHUNK", "1")
+    _lib.scan_fwd(x, a, b, c, y)  # launches fine; the error is found on the device
+    with pytest.raises(RuntimeError, match="expired"):
+        _lib.check_device_status(synchronize=True)
+    monkeypatch.delenv("QSSM_TEST_SKIP_FIRST_CHUNK")
+    _lib.scan_fwd(x, a, b, c, y)
+    _lib.check_device_status(synchronize=True)
+    ref = _oracle(inp, np.float64)
+    assert_close_f32(y, ref["y"], "y after the failed launch")
