@@ -1,6 +1,6 @@
 """The reference's own caller of the scan, ``quick_ssm/layers.py``, executed unmodified against
 this package (its ``from quick_ssm.scan_interface import scan`` resolves to our module).
-Needs the reference tree, which exists only in the build container; skipped elsewhere."""
+Needs a checkout of the reference next to this repository (or $QUICK_SSM_REFERENCE_DIR); skipped otherwise."""
 import importlib.util
 import os
 import sys
@@ -9,7 +9,10 @@ import types
 import pytest
 import torch
 
-REF = "/root/reference/quick_ssm/layers.py"
+# the reference checkout: $QUICK_SSM_REFERENCE_DIR, or a directory named "reference" next to this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_REF_DIR = os.environ.get("QUICK_SSM_REFERENCE_DIR", os.path.join(os.path.dirname(_REPO), "reference"))
+REF = os.path.join(_REF_DIR, "quick_ssm", "layers.py")
 pytestmark = pytest.mark.skipif(not os.path.exists(REF), reason="reference tree not present")
 
 
