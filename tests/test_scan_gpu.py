@@ -404,3 +404,26 @@ def test_expired_wait_is_reported_and_the_context_survives(monkeypatch):
     _lib.check_device_status(synchronize=True)
     ref = _oracle(inp, np.float64)
     assert_close_f32(y, ref["y"], "y after the failed launch")
+
+
+def test_views_with_odd_offsets_and_pitches():
+    """Batch, time and channel slices of larger tensors are scanned in place; a channel slice that
+    starts at an odd element (base not 16-byte aligned) takes the guarded path; results equal those
+    of contiguous copies."""
+    big = make_inputs(3, 120, 200, dtype=torch.bfloat16, seed=61).to(DEV)
+    for sl in [(slice(1, 3), slice(None), slice(None)),        # batch slice
+               (slice(None), slice(7, 100), slice(None)),      # time slice (still addressed in place)
+               (slice(None), slice(None), slice(1, 66)),       # odd channel offset: unaligned base
+               (slice(0, 2), slice(16, 48), slice(8, 136))]:   # all three, aligned
+        views = [t[sl] for t in big.tensors()]
+        dy = big.dy[sl]
+        outs = []
+        for tensors, g in ((views, dy), ([v.contiguous() for v in views], dy.contiguous())):
+            leaves = [t.detach().clone().requires_grad_() if t.is_contiguous() else t.detach().requires_grad_()
+                      for t in tensors]
+            y = scan(*leaves)
+            y.backward(g)
+            outs.append([y] + [t.grad for t in leaves])
+        for u, v in zip(*outs):
+            assert torch.equal(u, v)
+    _lib.check_device_status(synchronize=True)
