@@ -168,6 +168,36 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
                   int* status_word, void* stream);
 
 /*
+ * Scan with the gate activations of the SSM layer fused into its loads and stores.
+ * Inputs are the five projection outputs ("pre-activations") of the layer:
+ *     a = sigmoid(pa)   x = px   c = silu(pc1) * pc2   b = sigmoid(pd)     y = c * h
+ * each rounded to gate_dtype before use, as the layer rounds them to its compute dtype
+ * (reference: SSM.forward, layers.py:76-104; the element-wise kernels between the projections and
+ * scan() are what this replaces).  The backward returns the gradients of the five
+ * pre-activations (contiguous [B,L,D], in_dtype).  Supported: in fp32 with gates fp32/bf16/fp16
+ * and y, dy fp32; in bf16 (fp16) with gates bf16 (fp16) and y, dy bf16 (fp16) or fp32.
+ * All five inputs share one layout that the bulk copy engine can address (16-byte aligned base
+ * and pitches); otherwise QSSM_E_STRIDE is returned and the caller composes the gates itself.
+ * tile_h / h_in / h_last / g_in / g_first as in qssm_scan_fwd / qssm_scan_bwd.
+ */
+int qssm_gated_scan_fwd(const void* pa, const void* px, const void* pc1, const void* pc2, const void* pd,
+                        void* y, float* tile_h, const float* h_in, float* h_last,
+                        int64_t B, int64_t L, int64_t D,
+                        int64_t in_stride_b, int64_t in_stride_l,
+                        int64_t out_stride_b, int64_t out_stride_l,
+                        int in_dtype, int gate_dtype, int out_dtype,
+                        int* status_word, void* stream);
+
+int qssm_gated_scan_bwd(const void* pa, const void* px, const void* pc1, const void* pc2, const void* pd,
+                        const void* dy, const float* tile_h, const float* g_in, float* g_first,
+                        void* dpa, void* dpx, void* dpc1, void* dpc2, void* dpd,
+                        int64_t B, int64_t L, int64_t D,
+                        int64_t in_stride_b, int64_t in_stride_l,
+                        int64_t dy_stride_b, int64_t dy_stride_l,
+                        int in_dtype, int gate_dtype, int out_dtype,
+                        int* status_word, void* stream);
+
+/*
  * Aggregates of a whole [B,L,D] block, the values sequence shards exchange:
  *   forward : A[B,D] = prod_t a(t),  H[B,D] = h(L-1) computed from h(-1)=0,
  *             so that for any h_in  h(L-1) = A*h_in + H

@@ -35,6 +35,10 @@ SIGNATURES = {
                                 + [_c_vp, _c_vp]),
     "qssm_scan_bwd": (_c_int, [_c_vp] * 5 + [_c_vp] * 5 + [_c_vp] * 4 + [_c_vp, _c_sz] + [_c_i64] * 3
                       + [_c_i64] * 4 + [_c_int] * 3 + [_c_vp, _c_vp]),
+    "qssm_gated_scan_fwd": (_c_int, [_c_vp] * 6 + [_c_vp] * 3 + [_c_i64] * 3 + [_c_i64] * 4 + [_c_int] * 3
+                            + [_c_vp, _c_vp]),
+    "qssm_gated_scan_bwd": (_c_int, [_c_vp] * 6 + [_c_vp] * 3 + [_c_vp] * 5 + [_c_i64] * 3 + [_c_i64] * 4
+                            + [_c_int] * 3 + [_c_vp, _c_vp]),
     "qssm_scan_aggregate_fwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 2
                                 + [_c_int] * 2 + [_c_vp, _c_vp]),
     "qssm_scan_aggregate_bwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
@@ -221,6 +225,42 @@ def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=
                                   _ptr(ws), 0 if ws is None else ws.numel(), B, L, D, sb, sl, gb, gl,
                                   code_in, code_out, int(n_seg), _status_word(dev).data_ptr(), _stream(dev))
     _rc(rc, "qssm_scan_bwd")
+
+
+class Unsupported(RuntimeError):
+    """The fused-gate kernels cannot take these tensors (layout or dtype combination)."""
+
+
+def gated_scan_fwd(pa, px, pc1, pc2, pd, y, gate_dtype, *, tile_h=None, h_in=None, h_last=None) -> None:
+    dev = _require_cuda(pa, px, pc1, pc2, pd, y, tile_h, h_in, h_last)
+    B, L, D = pa.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        sb, sl = _blds(pa)
+        ob, ol = _blds(y)
+        rc = load().qssm_gated_scan_fwd(_ptr(pa), _ptr(px), _ptr(pc1), _ptr(pc2), _ptr(pd), _ptr(y), _ptr(tile_h),
+                                        _ptr(h_in), _ptr(h_last), B, L, D, sb, sl, ob, ol, dtype_code(pa.dtype),
+                                        dtype_code(gate_dtype), dtype_code(y.dtype),
+                                        _status_word(dev).data_ptr(), _stream(dev))
+    if rc in (-3, -4):
+        raise Unsupported(status_string(rc))
+    _rc(rc, "qssm_gated_scan_fwd")
+
+
+def gated_scan_bwd(pa, px, pc1, pc2, pd, dy, tile_h, grads, gate_dtype, *, g_in=None, g_first=None) -> None:
+    dev = _require_cuda(pa, px, pc1, pc2, pd, dy, tile_h, *grads)
+    B, L, D = pa.shape
+    check_device_status(dev)
+    with torch.cuda.device(dev):
+        sb, sl = _blds(pa)
+        gb, gl = _blds(dy)
+        rc = load().qssm_gated_scan_bwd(_ptr(pa), _ptr(px), _ptr(pc1), _ptr(pc2), _ptr(pd), _ptr(dy), _ptr(tile_h),
+                                        _ptr(g_in), _ptr(g_first), *[_ptr(t) for t in grads], B, L, D, sb, sl, gb, gl,
+                                        dtype_code(pa.dtype), dtype_code(gate_dtype), dtype_code(dy.dtype),
+                                        _status_word(dev).data_ptr(), _stream(dev))
+    if rc in (-3, -4):
+        raise Unsupported(status_string(rc))
+    _rc(rc, "qssm_gated_scan_bwd")
 
 
 def auto_segments(B: int, L: int, D: int, dtype: torch.dtype) -> int:

@@ -13,6 +13,7 @@ Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
   cfg3_stack 12 x layers.SSM (hidden 1024, state 4096, fp32 parameters, bf16 gates), B=16, L=4096,
              MSE loss to a random target: whole forward+backward step, with the time spent inside
              the scan kernels taken separately from CUDA events around every scan call
+  cfg3_gates the same scan shape with the layer's gate activations: fused kernels vs torch gates + scan
 With --shard the TOTAL problem is fixed and split over the ranks (strong scaling); the reported
 throughput is total elements over the slowest rank's device time.  One JSON line per run.
 """
@@ -43,6 +44,40 @@ def _median_ms(fn, steps, warmup, sync):
     e1.record()
     sync()
     return e0.elapsed_time(e1) / steps
+
+
+def run_gates(args):
+    """The scan of configuration 3 together with the layer's gate activations: fused kernels
+    (`gated_scan`) against torch element-wise gates followed by `scan`, forward + backward through
+    autograd, for fp32 projection outputs (fp32 parameters, the reference's setting) and bf16 ones."""
+    from .gated import _composed, gated_scan
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, D = 16, 4096, 4096
+    out = {"config": "cfg3_gates", "shape": [B, L, D], "gate_dtype": "bfloat16", "scan_out_dtype": "float32"}
+    for name, dtype in (("fp32_projections", torch.float32), ("bf16_projections", torch.bfloat16)):
+        torch.manual_seed(0)
+        pre = [torch.randn(B, L, D, device=dev, dtype=dtype) for _ in range(5)]
+        dy = torch.randn(B, L, D, device=dev)
+
+        def step(fn):
+            leaves = [t.detach().requires_grad_() for t in pre]
+            fn(leaves).backward(dy)
+
+        fused = _median_ms(lambda: step(lambda l: gated_scan(*l, gate_dtype=torch.bfloat16, out_dtype=torch.float32)),
+                           args.steps, args.warmup, torch.cuda.synchronize)
+        composed = _median_ms(lambda: step(lambda l: _composed(*l, torch.bfloat16, torch.float32)),
+                              args.steps, args.warmup, torch.cuda.synchronize)
+        s = pre[0].element_size()
+        out[name] = {"fused_ms": round(fused, 3), "torch_gates_plus_scan_ms": round(composed, 3),
+                     "speedup": round(composed / fused, 2),
+                     "fused_gelems": B * L * D / (fused * 1e-3) / 1e9,
+                     "fused_algorithmic_bytes_per_elem": 5 * s + 4 + 10 * s + 4}
+        del pre, dy
+        torch.cuda.empty_cache()
+    _lib.check_device_status(dev)
+    print(json.dumps(out), flush=True)
 
 
 def run_stack(args):
@@ -117,7 +152,7 @@ def run_stack(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack"])
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates"])
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
@@ -126,6 +161,8 @@ def main():
     args = ap.parse_args()
     if args.config == "cfg3_stack":
         return run_stack(args)
+    if args.config == "cfg3_gates":
+        return run_gates(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

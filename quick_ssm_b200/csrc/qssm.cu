@@ -41,6 +41,7 @@
 #include "qssm_agg.cuh"
 #include "qssm_bwd.cuh"
 #include "qssm_fwd.cuh"
+#include "qssm_gated.cuh"
 
 using namespace qssm;
 
@@ -899,6 +900,139 @@ int qssm_scan_aggregate_bwd(const void* a, const void* c, const void* dy, float*
                             int out_dtype, int n_seg, int* status_word, void* stream) {
     return aggregate_entry(true, a, c, dy, P, Q, ws, ws_bytes, B, L, D, in_stride_b, in_stride_l, dy_stride_b,
                            dy_stride_l, in_dtype, out_dtype, n_seg, status_word, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// scan with fused gate activations
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// Calls f(Tin{}, Tgate{}, Tout{}, Int<V>{}); Tout is the dtype of y / dy.
+template <typename F> int dispatch_gated(int in_dt, int gate_dt, int out_dt, int V, F&& f) {
+    auto with_v = [&](auto tin, auto tg, auto tout) -> int {
+        if (V == 1) return f(tin, tg, tout, Int<1>{});
+        return f(tin, tg, tout, Int<2>{});
+    };
+    if (in_dt == QSSM_F32 && out_dt == QSSM_F32) {
+        if (gate_dt == QSSM_F32) return with_v(float{}, float{}, float{});
+        if (gate_dt == QSSM_BF16) return with_v(float{}, __nv_bfloat16{}, float{});
+        if (gate_dt == QSSM_F16) return with_v(float{}, __half{}, float{});
+    }
+    if (in_dt == QSSM_BF16 && gate_dt == QSSM_BF16) {
+        if (out_dt == QSSM_BF16) return with_v(__nv_bfloat16{}, __nv_bfloat16{}, __nv_bfloat16{});
+        if (out_dt == QSSM_F32) return with_v(__nv_bfloat16{}, __nv_bfloat16{}, float{});
+    }
+    if (in_dt == QSSM_F16 && gate_dt == QSSM_F16) {
+        if (out_dt == QSSM_F16) return with_v(__half{}, __half{}, __half{});
+        if (out_dt == QSSM_F32) return with_v(__half{}, __half{}, float{});
+    }
+    return QSSM_E_DTYPE;
+}
+
+int check_gated(int64_t B, int64_t L, int64_t D, int in_dtype, int gate_dtype, int out_dtype) {
+    if (B < 0 || L < 0 || D < 0 || L >= (1ll << 31) - 64 || B >= (1ll << 31)) return QSSM_E_SHAPE;
+    if (dtype_size(in_dtype) == 0 || dtype_size(gate_dtype) == 0 || dtype_size(out_dtype) == 0) return QSSM_E_DTYPE;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qssm_gated_scan_fwd(const void* pa, const void* px, const void* pc1, const void* pc2, const void* pd, void* y,
+                        float* tile_h, const float* h_in, float* h_last, int64_t B, int64_t L, int64_t D,
+                        int64_t in_stride_b, int64_t in_stride_l, int64_t out_stride_b, int64_t out_stride_l,
+                        int in_dtype, int gate_dtype, int out_dtype, int* status_word, void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int rc = check_gated(B, L, D, in_dtype, gate_dtype, out_dtype);
+    if (rc) return rc;
+    if (B == 0 || L == 0 || D == 0) return 0;
+    if (pa == nullptr || px == nullptr || pc1 == nullptr || pc2 == nullptr || pd == nullptr || y == nullptr)
+        return QSSM_E_NULL;
+    if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
+    if ((rc = check_strides(L, D, out_stride_b, out_stride_l))) return rc;
+    const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+    const void* ins[5] = {pa, px, pc1, pc2, pd};
+    for (const void* t : ins)
+        if (!tma_ok(t, B, L, D, in_stride_b, in_stride_l, es)) return QSSM_E_STRIDE;
+    if (!tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo)) return QSSM_E_STRIDE;
+
+    Plan pl;
+    if ((rc = make_plan(pl, B, L, D, 1, status_word))) return rc;
+    GatedFwdParams fp;
+    memset(&fp, 0, sizeof(fp));
+    fp.g = pl.g;
+    const int chans = 32 * pl.V;
+    TensorDesc* descs[5] = {&fp.pa, &fp.px, &fp.pc1, &fp.pc2, &fp.pd};
+    for (int i = 0; i < 5; ++i)
+        if ((rc = fill_desc(*descs[i], ins[i], in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+    if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TS, true))) return rc;
+    fp.tile_h = tile_h;
+    fp.h_in = h_in;
+    fp.h_last = h_last;
+    const int stage = 5 * TS * chans * es;
+    const int outbuf = TS * chans * eo;
+    fp.g.n_out = 3;
+    fp.g.n_stages = pick_stages(pl.grid, stage, 2 * outbuf, 3 * outbuf, 2, 8, [](int ns) { return ns - 1; });
+    const int smem = fp.g.n_stages * stage + 3 * outbuf + MAX_STAGES * 8;
+    return dispatch_gated(in_dtype, gate_dtype, out_dtype, pl.V, [&](auto tin, auto tg, auto tout, auto v) -> int {
+        return launch(gated_fwd_kernel<decltype(tin), decltype(tg), decltype(tout), decltype(v)::value>, fp, pl.grid,
+                      smem, stream);
+    });
+}
+
+int qssm_gated_scan_bwd(const void* pa, const void* px, const void* pc1, const void* pc2, const void* pd,
+                        const void* dy, const float* tile_h, const float* g_in, float* g_first, void* dpa, void* dpx,
+                        void* dpc1, void* dpc2, void* dpd, int64_t B, int64_t L, int64_t D, int64_t in_stride_b,
+                        int64_t in_stride_l, int64_t dy_stride_b, int64_t dy_stride_l, int in_dtype, int gate_dtype,
+                        int out_dtype, int* status_word, void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int rc = check_gated(B, L, D, in_dtype, gate_dtype, out_dtype);
+    if (rc) return rc;
+    if (B == 0 || L == 0 || D == 0) return 0;
+    const void* ins[5] = {pa, px, pc1, pc2, pd};
+    void* outs[5] = {dpa, dpx, dpc1, dpc2, dpd};
+    for (int i = 0; i < 5; ++i)
+        if (ins[i] == nullptr || outs[i] == nullptr) return QSSM_E_NULL;
+    if (dy == nullptr) return QSSM_E_NULL;
+    if (tile_h == nullptr) return QSSM_E_NEED_H;
+    if ((rc = check_strides(L, D, in_stride_b, in_stride_l))) return rc;
+    if ((rc = check_strides(L, D, dy_stride_b, dy_stride_l))) return rc;
+    const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+    const long long g_sb = L * D, g_sl = D, n_tiles_b = (L + TS - 1) / TS;
+    for (int i = 0; i < 5; ++i)
+        if (!tma_ok(ins[i], B, L, D, in_stride_b, in_stride_l, es) || !tma_ok(outs[i], B, L, D, g_sb, g_sl, es))
+            return QSSM_E_STRIDE;
+    if (!tma_ok(dy, B, L, D, dy_stride_b, dy_stride_l, eo) || !tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4))
+        return QSSM_E_STRIDE;
+
+    Plan pl;
+    if ((rc = make_plan(pl, B, L, D, 1, status_word))) return rc;
+    pl.grid = concurrent_chains(pl.chains, true);
+    GatedBwdParams bp;
+    memset(&bp, 0, sizeof(bp));
+    bp.g = pl.g;
+    const int chans = 32 * pl.V;
+    TensorDesc* din[5] = {&bp.pa, &bp.px, &bp.pc1, &bp.pc2, &bp.pd};
+    TensorDesc* dout[5] = {&bp.dpa, &bp.dpx, &bp.dpc1, &bp.dpc2, &bp.dpd};
+    for (int i = 0; i < 5; ++i) {
+        if ((rc = fill_desc(*din[i], ins[i], in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
+        if ((rc = fill_desc(*dout[i], outs[i], in_dtype, B, L, D, g_sb, g_sl, chans, TS, true))) return rc;
+    }
+    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TS, true))) return rc;
+    if ((rc = fill_desc(bp.th, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, 1, true))) return rc;
+    bp.g_in = g_in;
+    bp.g_first = g_first;
+    const int stage = 5 * TS * chans * es + TS * chans * eo + ((chans * 4 + 127) / 128) * 128;
+    bp.g.n_stages = pick_stages(pl.grid, stage, 2 * 5 * TS * chans * es, 0, 2, 6,
+                                [](int ns) { return ns > 2 ? ns - 2 : 1; });
+    const int smem = bp.g.n_stages * stage + MAX_STAGES * 8;
+    return dispatch_gated(in_dtype, gate_dtype, out_dtype, pl.V, [&](auto tin, auto tg, auto tout, auto v) -> int {
+        return launch(gated_bwd_kernel<decltype(tin), decltype(tg), decltype(tout), decltype(v)::value>, bp, pl.grid,
+                      smem, stream);
+    });
 }
 
 int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k, int64_t n_chan, int64_t upto,

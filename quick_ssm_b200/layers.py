@@ -64,4 +64,25 @@ class SSM(nn.Module):
         return self.out_proj(h.to(self.out_proj.weight.dtype)) + skip
 
 
-__all__ = ["SSM", "RMSNorm"]
+class SSMFused(SSM):
+    """``SSM`` with the gate activations fused into the scan kernels (``gated.gated_scan``): same
+    parameters, same arguments, same result up to the rounding of the activations; the element-wise
+    kernels between the projections and the scan, and their backward, disappear."""
+
+    def forward(self, x: torch.Tensor, *, block_l: int = 256, checkpoint: bool = True,
+                tile_b: Optional[int] = None, tile_d: Optional[int] = None, backend: str = "auto",
+                scan_out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if backend == "torch" or x.device.type != "cuda" or not checkpoint:
+            return super().forward(x, block_l=block_l, checkpoint=checkpoint, tile_b=tile_b, tile_d=tile_d,
+                                   backend=backend, scan_out_dtype=scan_out_dtype)
+        from .gated import gated_scan
+        skip = x if self.use_residual else 0
+        u = self.pre_norm(x) if self.use_norm else x
+        if scan_out_dtype is None:
+            scan_out_dtype = self.out_proj.weight.dtype
+        h = gated_scan(self.A_proj(u), self.B_proj(u), self.C_proj_a(u), self.C_proj_b(u), self.D_proj(u),
+                       gate_dtype=self.compute_dtype, out_dtype=scan_out_dtype)
+        return self.out_proj(h.to(self.out_proj.weight.dtype)) + skip
+
+
+__all__ = ["SSM", "SSMFused", "RMSNorm"]

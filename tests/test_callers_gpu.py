@@ -126,3 +126,51 @@ def test_streaming_chunks_equal_one_scan():
         h_all, _ = scan_chunk(inp.x, inp.a, inp.b, None, ScanState.zeros(3, 72))
         assert torch.allclose(state.h, h_all[:, -1].float(), rtol=2e-2 if dtype != torch.float32 else 1e-5, atol=1e-3)
     _lib.check_device_status(synchronize=True)
+
+
+@pytest.mark.parametrize("param_dtype,compute_dtype", [(torch.float32, torch.bfloat16), (torch.float32, torch.float32),
+                                                      (torch.float32, torch.float16)],
+                         ids=["fp32_bf16", "fp32_fp32", "fp32_fp16"])
+def test_fused_gate_layer_matches_the_unfused_layer(param_dtype, compute_dtype):
+    """SSMFused reads the projection outputs in the scan kernels; output and every gradient must agree
+    with the unfused layer that builds the gates with torch element-wise kernels."""
+    from quick_ssm_b200.layers import SSMFused
+    torch.manual_seed(0)
+    ref = SSM(hidden_size=64, state_size_mult=4.0, dtype=param_dtype, compute_dtype=compute_dtype, device="cuda")
+    fused = SSMFused(hidden_size=64, state_size_mult=4.0, dtype=param_dtype, compute_dtype=compute_dtype, device="cuda")
+    fused.load_state_dict(ref.state_dict())
+    x = torch.randn(3, 300, 64, device="cuda", dtype=param_dtype)
+    outs = []
+    for layer in (ref, fused):
+        xi = x.clone().requires_grad_()
+        y = layer(xi, scan_out_dtype=torch.float32)
+        y.pow(2).mean().backward()
+        outs.append([y.detach(), xi.grad] + [p.grad for p in layer.parameters()])
+    _lib.check_device_status(synchronize=True)
+    tol = dict(rtol=2e-3, atol=2e-5) if compute_dtype == torch.float32 else dict(rtol=3e-2, atol=3e-4)
+    names = ["y", "dx"] + [n for n, _ in ref.named_parameters()]
+    for name, u, v in zip(names, *outs):
+        scale = float(u.abs().max())
+        assert torch.allclose(v, u, rtol=tol["rtol"], atol=tol["atol"] + 1e-2 * tol["rtol"] * scale), name
+
+
+def test_gated_scan_matches_composition_of_torch_gates():
+    from quick_ssm_b200.gated import _composed, gated_scan
+    torch.manual_seed(1)
+    for dtype, gate, out in [(torch.float32, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                             (torch.float16, torch.float16, torch.float32), (torch.float32, torch.float32, torch.float32)]:
+        pre = [torch.randn(2, 200, 136, device="cuda", dtype=dtype) for _ in range(5)]
+        dy = torch.randn(2, 200, 136, device="cuda", dtype=out)
+        res = []
+        for fn in (_composed, None):
+            leaves = [t.clone().requires_grad_() for t in pre]
+            y = fn(*leaves, gate, out) if fn else gated_scan(*leaves, gate_dtype=gate, out_dtype=out)
+            y.backward(dy)
+            res.append([y.detach()] + [t.grad for t in leaves])
+        _lib.check_device_status(synchronize=True)
+        for name, u, v in zip(("y", "dpa", "dpx", "dpc1", "dpc2", "dpd"), *res):
+            scale = float(u.float().abs().max())
+            assert torch.allclose(v.float(), u.float(), rtol=3e-2, atol=3e-3 * max(scale, 1.0)), (dtype, name)
+    # a layout the fused kernels cannot take falls back to the composed path on the GPU
+    odd = [torch.randn(1, 40, 7, device="cuda") for _ in range(5)]
+    assert torch.allclose(gated_scan(*odd), _composed(*odd, torch.float32, torch.float32), rtol=1e-4, atol=1e-5)
