@@ -174,3 +174,25 @@ def test_gated_scan_matches_composition_of_torch_gates():
     # a layout the fused kernels cannot take falls back to the composed path on the GPU
     odd = [torch.randn(1, 40, 7, device="cuda") for _ in range(5)]
     assert torch.allclose(gated_scan(*odd), _composed(*odd, torch.float32, torch.float32), rtol=1e-4, atol=1e-5)
+
+
+def test_gated_scan_fp32_against_float64_autograd():
+    """fp32 gates (no rounding, accurate sigmoid): forward and the five gradients against float64
+    autograd through the sequential loop on the CPU."""
+    from quick_ssm_b200 import scan
+    from quick_ssm_b200.gated import gated_scan
+    from tolerances import assert_close_f32
+    torch.manual_seed(3)
+    pre = [torch.randn(2, 150, 72) for _ in range(5)]
+    dy = torch.randn(2, 150, 72)
+    ref_leaves = [t.double().requires_grad_() for t in pre]
+    pa, px, pc1, pc2, pd = ref_leaves
+    y_ref = scan(px, torch.sigmoid(pa), torch.sigmoid(pd), torch.nn.functional.silu(pc1) * pc2, backend="torch")
+    y_ref.backward(dy.double())
+    leaves = [t.cuda().requires_grad_() for t in pre]
+    y = gated_scan(*leaves, gate_dtype=torch.float32, out_dtype=torch.float32)
+    y.backward(dy.cuda())
+    _lib.check_device_status(synchronize=True)
+    assert_close_f32(y, y_ref.detach(), "y")
+    for name, got, ref in zip(("dpa", "dpx", "dpc1", "dpc2", "dpd"), leaves, ref_leaves):
+        assert_close_f32(got.grad, ref.grad, name)
