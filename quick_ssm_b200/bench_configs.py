@@ -83,20 +83,22 @@ def run_gates(args):
 def run_stack(args):
     """Configuration 3: the scan inside a 12-layer SSM stack (projections stay torch GEMMs)."""
     from . import scan_interface
-    from .layers import SSM
+    from .gated import _GatedScanFunction
+    from .layers import SSM, SSMFused
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     torch.manual_seed(0)
     layers, hidden, B, L = 12, 1024, 16, 4096
-    stack = torch.nn.ModuleList([SSM(hidden_size=hidden, state_size_mult=4.0, dtype=torch.float32,
+    Layer = SSMFused if args.fused else SSM
+    stack = torch.nn.ModuleList([Layer(hidden_size=hidden, state_size_mult=4.0, dtype=torch.float32,
                                      compute_dtype=torch.bfloat16, device=dev) for _ in range(layers)])
     x = torch.randn(B, L, hidden, device=dev)
     target = torch.randn(B, L, hidden, device=dev)
 
     # CUDA events around every scan forward and backward
     events = []
-    fn = scan_interface._TritonScanFunction
+    fn = _GatedScanFunction if args.fused else scan_interface._TritonScanFunction
     orig_fwd, orig_bwd = fn.forward, fn.backward
 
     def timed(orig, kind):
@@ -139,7 +141,7 @@ def run_stack(args):
     scan_bwd_ms = sum(a.elapsed_time(b) for k, a, b in events if k == "bwd") / args.steps
     n = B * L * 4096
     print(json.dumps({
-        "config": "cfg3_stack", "layers": layers, "hidden": hidden, "state_dim": 4096, "B": B, "L": L,
+        "config": "cfg3_stack", "fused_gates": bool(args.fused), "layers": layers, "hidden": hidden, "state_dim": 4096, "B": B, "L": L,
         "compute_dtype": "bfloat16", "scan_out_dtype": "float32", "loss": float(loss.detach()),
         "step_ms": round(step_ms, 3), "scan_fwd_ms_per_step": round(scan_fwd_ms, 3),
         "scan_bwd_ms_per_step": round(scan_bwd_ms, 3),
@@ -158,6 +160,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--segments", type=int, default=0, help="time segments per GPU (0 = automatic)")
+    ap.add_argument("--fused", action="store_true", help="cfg3_stack: SSMFused layers (gates inside the scan kernels)")
     args = ap.parse_args()
     if args.config == "cfg3_stack":
         return run_stack(args)
