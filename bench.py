@@ -291,7 +291,7 @@ def run_gpu(args):
             "config": {"workload": WORKLOAD, "B": B, "L": L, "D": D, "accumulate": "fp32", "checkpoint": True,
                        "per_rank": "every rank scans its own B x L x D shard (no data-path collective)",
                        "l2": "no flush needed: each step streams 7.5 GB of distinct tensors, far above the 126 MB L2"},
-            "roofline": {"bound": "hbm", "kernel": "scan_bwd_kernel", "achieved": bwd_gbs, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "scan_bwd_tile4_kernel", "achieved": bwd_gbs, "peak": peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s",
                          "frac": bwd_gbs / peak, "traffic": NCU_BWD_TRAFFIC_BYTES_L2048 * (L / 2048),
                          "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,

@@ -212,7 +212,8 @@ size_t ws_bytes_for(long long B, long long D, int n_seg) {
 //   fixed_bytes   shared memory besides the input stages
 //   prefetch(ns)  input tiles in flight with ns stages
 template <typename F>
-int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_bytes, int lo, int hi, F prefetch) {
+int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_bytes, int lo, int hi, F prefetch,
+                long long total_budget = 15ll << 20) {
     const int forced = env_int("QSSM_STAGES", 0);
     if (forced >= lo && forced <= MAX_STAGES &&
         (long long)forced * stage_bytes + fixed_bytes + MAX_STAGES * 8 <= 227 * 1024)
@@ -220,7 +221,7 @@ int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_byte
     const long long sms = sm_count();
     const long long per_sm = (grid + sms - 1) / sms;
     const long long smem_cap = (228 * 1024) / (per_sm < 1 ? 1 : per_sm) - 1024;
-    const long long budget = (15ll << 20) / (grid < 1 ? 1 : grid);
+    const long long budget = total_budget / (grid < 1 ? 1 : grid);
     int best = lo;
     for (int ns = lo; ns <= hi; ++ns) {
         const long long smem = (long long)ns * stage_bytes + fixed_bytes + MAX_STAGES * 8;
@@ -792,7 +793,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     else
         rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, TB / TS, tma);
     if (rc) return rc;
-    // Four adjacent strips per CTA with one store per gradient tensor (16-bit storage, full-width rows).
+    // Four adjacent strips per CTA, loaded and stored as one 512-byte-wide tile per tensor (16-bit storage).
     // One such CTA fits per SM, so the groups must fill whole rounds of SM-count CTAs reasonably well;
     // otherwise (e.g. 152 groups on 148 SMs) the one-warp-per-CTA kernel, which packs finer, is used.
     bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W;
@@ -802,6 +803,19 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
         if ((double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
     }
     const int out_box = wide ? WIDE_W * chans : chans;
+    if (wide) {  // re-encode the inputs with four-strip boxes
+        const int box = WIDE_W * chans;
+        if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, box, TB, tma))) return rc;
+        if (saved)
+            rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, box, TB + 1, tma);
+        else
+            rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, box, 1, tma);
+        if (rc) return rc;
+    }
     if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
     if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
     if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
@@ -815,25 +829,21 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     const int stage = 4 * TB * chans * es + TB * chans * eo + ((h_tile + 127) / 128) * 128;
     const int grad_tile = 4 * TB * chans * es;  // the four gradient tiles of one strip
     if (wide) {
-        const int n_dgroups = (pl.g.n_dtiles + WIDE_W - 1) / WIDE_W;
-        const long long n_groups = B * n_seg * n_dgroups;
+        const long long n_groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
         const long long wide_rounds = (n_groups + sm_count() - 1) / sm_count();
-        long long ctas = (n_groups + wide_rounds - 1) / wide_rounds;  // equal rounds, at most one CTA per SM
-        int n_out = env_int("QSSM_NOUT_BWD", 2);
-        if (n_out < 2) n_out = 2;
-        if (n_out > 3) n_out = 3;
-        bp.g.n_out = n_out;
-        const int outbuf = WIDE_W * grad_tile;
-        bp.g.n_stages = pick_stages(ctas, WIDE_W * stage, (n_out - 1) * outbuf,
-                                    n_out * outbuf + WIDE_W * MAX_STAGES * 8, 2, 6, [](int ns) { return ns - 1; });
-        const int smem = WIDE_W * bp.g.n_stages * stage + n_out * outbuf + WIDE_W * MAX_STAGES * 8;
+        const long long ctas = (n_groups + wide_rounds - 1) / wide_rounds;  // equal rounds, at most one CTA per SM
+        const int stage4 = WIDE_W * (4 * TB * chans * es + TB * chans * eo + h_tile);
+        // measured: with CTA-wide tiles the best depth corresponds to about 20 MB in flight
+        // (cfg1, 128 CTAs: 4 stages 0.755 ms, 3 stages 0.820 ms; cfg4, 147 CTAs: 3 stages 6.28 ms, 4 stages 6.59 ms)
+        bp.g.n_stages = pick_stages(ctas, stage4, 2 * WIDE_W * grad_tile, 0, 2, 5,
+                                    [](int ns) { return ns > 2 ? ns - 2 : 1; }, 20ll << 20);
+        const int smem = bp.g.n_stages * stage4 + MAX_STAGES * 8;
         return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
             using Tin = decltype(tin);
             using Tout = decltype(tout);
             if constexpr (sizeof(Tin) == 2) {
-                if (saved)
-                    return launch(scan_bwd_wide_kernel<Tin, Tout, 2, true>, bp, ctas, smem, stream, 32 * WIDE_W);
-                return launch(scan_bwd_wide_kernel<Tin, Tout, 2, false>, bp, ctas, smem, stream, 32 * WIDE_W);
+                if (saved) return launch(scan_bwd_tile4_kernel<Tin, Tout, true>, bp, ctas, smem, stream, 32 * WIDE_W);
+                return launch(scan_bwd_tile4_kernel<Tin, Tout, false>, bp, ctas, smem, stream, 32 * WIDE_W);
             } else {
                 return QSSM_E_DTYPE;
             }

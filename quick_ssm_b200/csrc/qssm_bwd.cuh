@@ -1,6 +1,6 @@
 // Backward kernels: one warp per chain with in-place gradient stores (scan_bwd_kernel), the chained
-// single-pass variant (scan_bwd_chained_kernel) and four strips per CTA with combined 512-byte-wide
-// stores (scan_bwd_wide_kernel).
+// single-pass variant (scan_bwd_chained_kernel) and four strips per CTA on shared 512-byte-wide
+// tiles (scan_bwd_tile4_kernel).
 #pragma once
 #include "qssm_fwd.cuh"
 
@@ -13,26 +13,28 @@ namespace qssm {
 // ---------------------------------------------------------------------------------------------
 // Results go to (ox, oa, ob, oc), tiles whose rows hold OSTRIDE lane-vectors; `ocol` is this warp's first
 // column in such a row.  In-place operation passes the input tiles again with OSTRIDE = 32, ocol = 0.
-template <typename Tin, typename Tdy, int V, bool SAVED_H, bool FULL, int OSTRIDE = 32>
+// Input tiles have rows of ISTRIDE lane-vectors and this warp starts at column `icol` of a row
+// (32 and 0 when the tile belongs to the warp alone).
+template <typename Tin, typename Tdy, int V, bool SAVED_H, bool FULL, int OSTRIDE = 32, int ISTRIDE = 32>
 __device__ __forceinline__ void bwd_batch(const unsigned char* sx, const unsigned char* sa, const unsigned char* sb,
                                           const unsigned char* sc, const unsigned char* sg, const unsigned char* sh,
                                           unsigned char* ox, unsigned char* oa, unsigned char* ob, unsigned char* oc,
                                           int ocol, int lane, int nrows, bool first_rows, const float* h_in_lane,
-                                          long long d_lane, long long D, float (&G)[V]) {
+                                          long long d_lane, long long D, float (&G)[V], int icol = 0) {
     Vec<Tin, V> xw[TS], aw[TS], bw[TS], cw[TS];
     Vec<Tdy, V> gw[TS];
 #pragma unroll
     for (int r = 0; r < TS; ++r) {
-        xw[r] = tile_raw<Tin, V>(sx, r, lane);
-        aw[r] = tile_raw<Tin, V>(sa, r, lane);
-        bw[r] = tile_raw<Tin, V>(sb, r, lane);
+        xw[r] = reinterpret_cast<const Vec<Tin, V>*>(sx)[(r) * ISTRIDE + icol + lane];
+        aw[r] = reinterpret_cast<const Vec<Tin, V>*>(sa)[(r) * ISTRIDE + icol + lane];
+        bw[r] = reinterpret_cast<const Vec<Tin, V>*>(sb)[(r) * ISTRIDE + icol + lane];
     }
     // h(t0-1 .. t0+TS-1): entry 0 is the state before the batch
     float hreg[TS + 1][V];
     if (SAVED_H) {
 #pragma unroll
         for (int r = 0; r <= TS; ++r) {
-            const Vec<float, V> w = tile_raw<float, V>(sh, r, lane);
+            const Vec<float, V> w = reinterpret_cast<const Vec<float, V>*>(sh)[(r) * ISTRIDE + icol + lane];
             unpack<float, V>(w, hreg[r]);
         }
         if (first_rows && h_in_lane != nullptr) {
@@ -40,13 +42,13 @@ __device__ __forceinline__ void bwd_batch(const unsigned char* sx, const unsigne
             for (int i = 0; i < V; ++i) hreg[0][i] = (d_lane + i < D) ? h_in_lane[i] : 0.f;
         }
     } else {
-        const Vec<float, V> w = tile_raw<float, V>(sh, 0, lane);
+        const Vec<float, V> w = reinterpret_cast<const Vec<float, V>*>(sh)[(0) * ISTRIDE + icol + lane];
         unpack<float, V>(w, hreg[0]);
     }
 #pragma unroll
     for (int r = 0; r < TS; ++r) {
-        cw[r] = tile_raw<Tin, V>(sc, r, lane);
-        gw[r] = tile_raw<Tdy, V>(sg, r, lane);
+        cw[r] = reinterpret_cast<const Vec<Tin, V>*>(sc)[(r) * ISTRIDE + icol + lane];
+        gw[r] = reinterpret_cast<const Vec<Tdy, V>*>(sg)[(r) * ISTRIDE + icol + lane];
     }
     if (!SAVED_H) {
 #pragma unroll
@@ -460,50 +462,45 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward with combined stores: a CTA of W = 4 warps scans four adjacent channel strips of the
-// same batch entry and time range.  Every warp keeps its own input ring (no coupling on the load
-// side); the gradients of a tile go to a shared staging tile 4 strips wide and ONE bulk store per
-// gradient tensor writes 512 contiguous bytes per row instead of four stores of 128 bytes from
-// four unrelated CTAs.  Measured on B200 the write-heavy backward gains from that locality: with
-// 128-byte-wide stores it moves 5.9 TB/s, with contiguous rows 6.3-6.45 TB/s.
-// One __syncthreads per tile orders "all four strips written" before the store is issued.
+// backward on shared 4-strip tiles (16-bit storage, D > 192): a CTA of W = 4 warps scans four adjacent
+// channel strips of the same batch entry and time range as ONE tile - one bulk copy of 16 rows x
+// 512 bytes per tensor in, gradients written in place, one bulk copy per gradient tensor out.
+// The write-heavy backward gains from that contiguity: on B200, cfg1, one warp per CTA with
+// 128-byte-wide copies moves 5.9 TB/s, four strips with only the stores combined 6.17 TB/s, this
+// kernel 6.41 TB/s (on a layout whose strips are contiguous in memory, D = 64, the narrow kernel also
+// reaches 6.46 TB/s).  One ring of stages and one mbarrier per stage for the whole CTA; thread 0
+// issues every copy; one __syncthreads per tile orders "four strips written" before the store.
 // ---------------------------------------------------------------------------------------------
 constexpr int WIDE_W = 4;
 
-template <typename Tin, typename Tdy, int V, bool SAVED_H>
-__global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid_constant__ BwdParams p) {
+template <typename Tin, typename Tdy, bool SAVED_H>
+__global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_tile4_kernel(const __grid_constant__ BwdParams p) {
     constexpr int W = WIDE_W;
+    constexpr int V = 2;
     constexpr int TB = TS;
     constexpr int DT = 32 * V;
-    constexpr int IN_ROW = 32 * V * (int)sizeof(Tin);
-    constexpr int DY_ROW = 32 * V * (int)sizeof(Tdy);
-    constexpr int H_ROW = 32 * V * 4;
-    constexpr int IN_TILE = TB * IN_ROW;
-    constexpr int DY_TILE = TB * DY_ROW;
+    constexpr int LANES = 32 * W;  // lane-vectors per tile row
+    constexpr int IN_TILE = TB * LANES * V * (int)sizeof(Tin);
+    constexpr int DY_TILE = TB * LANES * V * (int)sizeof(Tdy);
+    constexpr int H_ROW = LANES * V * 4;
     constexpr int H_TILE = SAVED_H ? (TB + 1) * H_ROW : H_ROW;
-    constexpr int H_SLOT = ((H_TILE + 127) / 128) * 128;
-    constexpr int STAGE = 4 * IN_TILE + DY_TILE + H_SLOT;
+    constexpr int STAGE = 4 * IN_TILE + DY_TILE + H_TILE;
     constexpr int OFF_DY = 4 * IN_TILE;
     constexpr int OFF_H = OFF_DY + DY_TILE;
-    constexpr int OUT_TILE = TB * W * IN_ROW;  // one gradient tensor, four strips wide
-    constexpr int OUTBUF = 4 * OUT_TILE;
 
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_fail;
     const Geom& g = p.g;
     const int NS = g.n_stages;
-    const int NOUT = g.n_out;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    unsigned char* const my_stages = smem + (size_t)warp * NS * STAGE;
-    unsigned char* const outbuf = smem + (size_t)W * NS * STAGE;
-    const uint32_t bars = smem_u32(outbuf + (size_t)NOUT * OUTBUF) + warp * MAX_STAGES * 8;
-    const uint32_t my_base = smem_u32(my_stages);
+    const uint32_t bars = smem_u32(smem + (size_t)NS * STAGE);
+    const uint32_t smem_base = smem_u32(smem);
     const bool ld_hint = (g.l2_hint & 1) != 0, st_hint = (g.l2_hint & 2) != 0;
     const uint64_t pol = l2_policy_evict_first();
 
-    if (threadIdx.x == 0) s_fail = 0;
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
+        s_fail = 0;
         for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
         fence_barrier_init();
     }
@@ -511,9 +508,8 @@ __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid
 
     const int n_dgroups = (g.n_dtiles + W - 1) / W;
     const long long n_groups = g.B * g.n_seg * n_dgroups;
-    RingPos pf{0, 0};
-    RingPos cur{0, 0};
-    int oslot = 0;
+    const int PF = NS > 2 ? NS - 2 : 1;
+    RingPos pf{0, 0}, cur{0, 0};
     bool failed = false;
     for (long long gid = blockIdx.x; gid < n_groups && !failed; gid += gridDim.x) {
         const long long dgroup = gid % n_dgroups;
@@ -521,7 +517,6 @@ __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid
         const int seg = (int)(rest % g.n_seg);
         const long long b = rest / g.n_seg;
         const long long d0 = (dgroup * W + warp) * DT;
-        const bool active = d0 < g.D;  // the last group of a row may have fewer than four strips
         const long long t_begin = (long long)seg * g.seg_rows;
         long long t_end = t_begin + g.seg_rows;
         if (t_end > g.L) t_end = g.L;
@@ -531,7 +526,7 @@ __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid
         float G[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) G[i] = 0.f;
-        if (active && p.g_in != nullptr) {
+        if (p.g_in != nullptr) {
             const float* src = p.g_in + (b * g.n_seg + seg) * g.D;
 #pragma unroll
             for (int i = 0; i < V; ++i)
@@ -539,14 +534,17 @@ __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid
         }
         const float* h_in_lane = (SAVED_H && p.h_in != nullptr) ? p.h_in + b * g.D + d_lane : nullptr;
 
-        const int c0 = (int)d0, c2 = (int)b, c0_wide = (int)(dgroup * W * DT);
+        const int c0 = (int)(dgroup * W * DT), c2 = (int)b;
         int pf_row = (int)(t_begin + (long long)(n_tiles - 1) * TB);
-        int pf_left = active ? n_tiles : 0;
-        auto issue = [&]() {
-            const uint32_t st = my_base + pf.s * STAGE;
+        int pf_left = n_tiles;
+        auto issue = [&]() {  // thread 0 only
+            const uint32_t st = smem_base + pf.s * STAGE;
             const uint32_t bar = bars + 8 * pf.s;
+            // gradients are stored from the stage: it is refilled only when that store has drained
+            if (NS > 2) tma_wait_read<1>();
+            else tma_wait_read<0>();
             fence_proxy_async();
-            mbar_expect_tx(bar, 4 * IN_TILE + DY_TILE + H_TILE);
+            mbar_expect_tx(bar, STAGE);
             tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2, ld_hint, pol);
             tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2, ld_hint, pol);
             tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2, ld_hint, pol);
@@ -560,59 +558,52 @@ __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_wide_kernel(const __grid
             pf_row -= TB;
             --pf_left;
         };
-        if (lane == 0) {
-            for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
+        if (threadIdx.x == 0) {
+            for (int k = 0; k < PF && pf_left > 0; ++k) issue();
         }
 
         long long t0 = t_begin + (long long)(n_tiles - 1) * TB;
         for (int j = 0; j < n_tiles; ++j, t0 -= TB) {
-            unsigned char* ob = outbuf + (size_t)oslot * OUTBUF;
-            if (active) {
-                const unsigned char* st = my_stages + cur.s * STAGE;
-                const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
-                if (lane == 0 && pf_left > 0) issue();
-                bool ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    if (lane == 0) s_fail = 1;
-                } else {
-                    const bool first_rows = (t0 == 0);
-                    if (nrows >= TS)
-                        bwd_batch<Tin, Tdy, V, SAVED_H, true, 32 * W>(
-                            st, st + IN_TILE, st + 2 * IN_TILE, st + 3 * IN_TILE, st + OFF_DY, st + OFF_H, ob,
-                            ob + OUT_TILE, ob + 2 * OUT_TILE, ob + 3 * OUT_TILE, warp * 32, lane, TS, first_rows,
-                            h_in_lane, d_lane, g.D, G);
-                    else
-                        bwd_batch<Tin, Tdy, V, SAVED_H, false, 32 * W>(
-                            st, st + IN_TILE, st + 2 * IN_TILE, st + 3 * IN_TILE, st + OFF_DY, st + OFF_H, ob,
-                            ob + OUT_TILE, ob + 2 * OUT_TILE, ob + 3 * OUT_TILE, warp * 32, lane, nrows, first_rows,
-                            h_in_lane, d_lane, g.D, G);
-                }
-                cur.advance(NS);
+            unsigned char* st = smem + cur.s * STAGE;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (threadIdx.x == 0 && pf_left > 0) issue();
+            bool ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) s_fail = 1;
+            } else {
+                unsigned char* sx = st;
+                unsigned char* sa = st + IN_TILE;
+                unsigned char* sb = st + 2 * IN_TILE;
+                unsigned char* sc = st + 3 * IN_TILE;
+                const bool first_rows = (t0 == 0);
+                if (nrows >= TS)
+                    bwd_batch<Tin, Tdy, V, SAVED_H, true, LANES, LANES>(sx, sa, sb, sc, st + OFF_DY, st + OFF_H, sx, sa,
+                                                                        sb, sc, warp * 32, lane, TS, first_rows,
+                                                                        h_in_lane, d_lane, g.D, G, warp * 32);
+                else
+                    bwd_batch<Tin, Tdy, V, SAVED_H, false, LANES, LANES>(sx, sa, sb, sc, st + OFF_DY, st + OFF_H, sx,
+                                                                         sa, sb, sc, warp * 32, lane, nrows, first_rows,
+                                                                         h_in_lane, d_lane, g.D, G, warp * 32);
             }
             fence_proxy_async();
-            // the staging tile written NOUT - 1 tiles from now must be free: stores older than that have drained
-            if (threadIdx.x == 0) {
-                if (NOUT == 2) tma_wait_read<0>();
-                else tma_wait_read<1>();
-            }
             __syncthreads();
             if (s_fail != 0) {
                 failed = true;
                 break;
             }
             if (threadIdx.x == 0) {
-                const uint32_t so = smem_u32(ob);
-                tma_st(&p.dx.map, so + 0 * OUT_TILE, c0_wide, (int)t0, c2, st_hint, pol);
-                tma_st(&p.da.map, so + 1 * OUT_TILE, c0_wide, (int)t0, c2, st_hint, pol);
-                tma_st(&p.db.map, so + 2 * OUT_TILE, c0_wide, (int)t0, c2, st_hint, pol);
-                tma_st(&p.dc.map, so + 3 * OUT_TILE, c0_wide, (int)t0, c2, st_hint, pol);
+                const uint32_t sst = smem_base + cur.s * STAGE;
+                tma_st(&p.dx.map, sst + 0 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.da.map, sst + 1 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.db.map, sst + 2 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
+                tma_st(&p.dc.map, sst + 3 * IN_TILE, c0, (int)t0, c2, st_hint, pol);
                 tma_commit();
             }
-            if (++oslot == NOUT) oslot = 0;
+            cur.advance(NS);
         }
         if (failed) break;
-        if (active && p.g_first != nullptr && seg == 0) {
+        if (p.g_first != nullptr && seg == 0) {
             float* dst = p.g_first + b * g.D;
 #pragma unroll
             for (int i = 0; i < V; ++i)
