@@ -37,7 +37,7 @@ WORKLOAD = "cfg1: scan fwd+bwd, B=8 L=8192 D=4096, bf16 storage / fp32 accumulat
 # DRAM bytes (read + write) of one backward launch, from an ncu capture of the same kernel on a
 # quarter of the sequence (`--seq-len 2048`: same chains, same residency, 1.3 GB resident);
 # traffic grows in proportion to L, so a full launch is this times L/2048.
-NCU_BWD_TRAFFIC_BYTES_L2048 = 687.97e6 + 494.12e6
+NCU_BWD_TRAFFIC_BYTES_L2048 = 687.91e6 + 492.08e6
 
 
 def _peak_hbm():

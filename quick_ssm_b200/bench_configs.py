@@ -161,6 +161,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--segments", type=int, default=0, help="time segments per GPU (0 = automatic)")
     ap.add_argument("--fused", action="store_true", help="cfg3_stack: SSMFused layers (gates inside the scan kernels)")
+    ap.add_argument("--seq-len", type=int, default=0, help="override L (a small case of the same kernels for a profiler)")
     args = ap.parse_args()
     if args.config == "cfg3_stack":
         return run_stack(args)
@@ -176,7 +177,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     cfg = dict(CONFIGS[args.config])
-    B, L, D = cfg["B"], cfg["L"], cfg["D"]
+    B, L, D = cfg["B"], args.seq_len or cfg["L"], cfg["D"]
     total = B * L * D
     if args.shard == "batch":
         assert B % world == 0, "batch must divide over the ranks"

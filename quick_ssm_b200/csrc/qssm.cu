@@ -410,7 +410,9 @@ ChainedLayout chained_layout(long long B, long long L, long long D, int elem_siz
     const long long total = c.n_chains * c.n_chunks;
     if (c.grid > total) c.grid = total;
     if (c.grid < 1) c.grid = 1;
-    long long need = (c.grid + c.n_chains - 1) / c.n_chains + 2;  // chunks of one chain in flight, plus slack
+    // chunks of one chain in flight, plus slack; the kernels check before they reuse a slot, so a ring
+    // that is too small (one chain far behind the others) costs waiting, not correctness
+    long long need = (c.grid + c.n_chains - 1) / c.n_chains + 8;
     int slots = 4;
     while (slots < need) slots <<= 1;
     c.slots = slots;

@@ -404,6 +404,8 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
             for (int i = 0; i < V; ++i)
                 G[i] = (p.g_in != nullptr && d_lane + i < g.D) ? p.g_in[b * g.D + d_lane + i] : 0.f;
         } else {
+            ok = chained_slot_free(cdesc, cp.slots, kk, lane, cp.wait_ns);
+            if (!ok) break;
             __stcg(mydesc + lane, make_float4(mytag, P[0], P[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, Q[0], Q[1], 0.f));
             ok = chained_lookback(cdesc, cp.slots, kk, lane, cp.wait_ns, G);

@@ -212,6 +212,25 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
     if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
 }
 
+// Before chunk k (processing order) writes its descriptor into slot k mod slots it makes sure the
+// previous owner of that slot, chunk k - slots, is no longer needed: once chunk k - slots + 1 has
+// published its inclusive state, every later chunk finds that state (or a nearer one) before it would
+// look at chunk k - slots.  Almost always true at once; the wait is bounded like every other.
+__device__ __forceinline__ bool chained_slot_free(const float4* cdesc, int slots, long long k, int lane,
+                                                  unsigned long long wait_ns) {
+    const long long j = k - slots + 1;
+    if (j < 0) return true;
+    const float4* dj = cdesc + (size_t)(j & (slots - 1)) * 96 + 64 + lane;
+    const unsigned int want = (unsigned int)(j + 1);
+    if (__all_sync(0xffffffffu, __float_as_uint(__ldcg(dj).x) == want)) return true;
+    const unsigned long long start = global_timer_ns();
+    for (unsigned int it = 0;; ++it) {
+        if (__all_sync(0xffffffffu, __float_as_uint(__ldcg(dj).x) == want)) return true;
+        __nanosleep(100);
+        if ((it & 255u) == 255u && __any_sync(0xffffffffu, global_timer_ns() - start > wait_ns)) return false;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Look-back over the chunk descriptors of one chain (chained kernels).
 //
@@ -232,7 +251,8 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                                                  unsigned long long wait_ns, float (&h)[2]) {
     constexpr int WIN = 8;
     bool ok = true;
-    long long js = -1;  // nearest predecessor whose inclusive end state is known
+    long long js = -1;      // nearest predecessor whose inclusive end state is known
+    long long folded = 0;   // aggregates of chunks js+1 .. folded-1 are already applied to h
     for (long long top = k - 1; js < 0 && ok; top -= WIN) {
         float4 wi[WIN], wa[WIN], wh[WIN];
 #pragma unroll
@@ -276,10 +296,21 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                 js = j;
             }
         }
+        if (ok && js >= 0) {  // the aggregates of this window that lie after js are in registers: apply them now
+            const int qf = (int)(top - js);
+#pragma unroll
+            for (int q = WIN - 1; q >= 0; --q) {
+                if (q < qf) {
+                    h[0] = fmaf(wa[q].y, h[0], wh[q].y);
+                    h[1] = fmaf(wa[q].z, h[1], wh[q].z);
+                }
+            }
+            folded = top + 1;
+        }
     }
     if (!ok) return false;
-    // forward through the aggregates of chunks js+1 .. k-1 (all seen published above)
-    for (long long base = js + 1; base < k; base += WIN) {
+    // forward through the aggregates of the nearer windows, chunks folded .. k-1 (all seen published above)
+    for (long long base = folded; base < k; base += WIN) {
         float4 wa[WIN], wh[WIN];
 #pragma unroll
         for (int q = 0; q < WIN; ++q) {
@@ -430,6 +461,8 @@ __global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_const
             for (int i = 0; i < V; ++i)
                 h[i] = (p.h_in != nullptr && d_lane + i < g.D) ? p.h_in[b * g.D + d_lane + i] : 0.f;
         } else {
+            ok = chained_slot_free(cdesc, cp.slots, k, lane, cp.wait_ns);
+            if (!ok) break;
             __stcg(mydesc + lane, make_float4(mytag, A[0], A[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, H[0], H[1], 0.f));
             ok = chained_lookback(cdesc, cp.slots, k, lane, cp.wait_ns, h);
