@@ -233,8 +233,10 @@ def run_gpu(args):
         barrier()
     _lib.check_device_status(dev)
     total_ms = t_begin.elapsed_time(t_end)
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    fwd_all = sorted(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_all = sorted(e[1].elapsed_time(e[2]) for e in ev)
+    fwd_ms = sum(fwd_all) / K
+    bwd_ms = sum(bwd_all) / K
 
     if args.no_e2e:
         if rank == 0:
@@ -269,11 +271,20 @@ def run_gpu(args):
     same = _close(host["dx"][-1].to(dev), grads[0][-1]) and _close(host["y"][0].to(dev), y[0])
     if not same:
         raise SystemExit("e2e host-buffer path disagrees with the device-resident path")
+    # the same copies without the kernels: the time the transfers alone take (not part of any bench value)
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        done = pipe.run(host, compute=False)
+    torch.cuda.current_stream(dev).wait_event(done)
+    e1.record()
+    barrier()
+    copy_only_ms = e0.elapsed_time(e1) / e2e_steps
 
     if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms, copy_only_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, fwd_ms, bwd_ms = (float(v) for v in t.tolist())
+        total_ms, e2e_ms, fwd_ms, bwd_ms, copy_only_ms = (float(v) for v in t.tolist())
 
     if rank == 0:
         ms_per_step = total_ms / K
@@ -295,13 +306,16 @@ def run_gpu(args):
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s",
                          "frac": bwd_gbs / peak, "traffic": NCU_BWD_TRAFFIC_BYTES_L2048 * (L / 2048),
                          "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
+                         "ms_min_median_max": [bwd_all[0], bwd_all[K // 2], bwd_all[-1]],
                          "fwd": {"kernel": "scan_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
-                                 "algorithmic_bytes": fwd_bytes, "ms": fwd_ms},
+                                 "algorithmic_bytes": fwd_bytes, "ms": fwd_ms,
+                                 "ms_min_median_max": [fwd_all[0], fwd_all[K // 2], fwd_all[-1]]},
                          "step": {"achieved": step_gbs, "frac": step_gbs / peak,
                                   "roofline_gelems": peak / (14 * es)}},
             "e2e": {"value": world * n_elem / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "transfers_alone_ms_per_step": copy_only_ms,
                     "path": "quick_ssm_b200.host.HostScan: pinned host buffers -> H2D -> qssm_scan_fwd/bwd -> D2H"},
             "gpu_launches": 2 * K * world,
             "gpu_launches_e2e": e2e_launches * world,

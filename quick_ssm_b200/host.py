@@ -68,11 +68,14 @@ class HostScan:
     def d2h_bytes(self) -> int:
         return self.h2d_bytes  # y in out_dtype + four gradients in the input dtype
 
-    def run(self, host: Dict[str, torch.Tensor]) -> torch.cuda.Event:
+    def run(self, host: Dict[str, torch.Tensor], compute: bool = True) -> torch.cuda.Event:
         """Enqueue one forward+backward over ``host`` (see ``alloc_pinned``) and return the event that
         marks its last device->host copy.  The call does not wait: the caller synchronises on the
         event (or the device) before reading the results.  The input buffers must stay unchanged
-        until then; consecutive calls overlap their transfers."""
+        until then; consecutive calls overlap their transfers.
+
+        ``compute=False`` runs the same copies without the kernels - the transfer-only time the
+        pipeline cannot beat, for benchmarks."""
         cur = torch.cuda.current_stream(self.device)
         self.s_in.wait_stream(cur)  # whatever produced the host-visible inputs on this stream
         drained, computed = self._drained, self._computed
@@ -95,10 +98,11 @@ class HostScan:
                 if drained[k] is not None:
                     self.s_k.wait_event(drained[k])  # results of this set have left the device
                 v = {name: t[:n] for name, t in dev.items()}
-                _lib.scan_fwd(v["x"], v["a"], v["b"], v["c"], v["y"], tile_h=v["tile_h"])
-                _lib.scan_bwd(v["x"], v["a"], v["b"], v["c"], v["dy"], v["dx"], v["da"], v["db"], v["dc"],
-                              tile_h=v["tile_h"])
-                self.kernel_launches += 2
+                if compute:
+                    _lib.scan_fwd(v["x"], v["a"], v["b"], v["c"], v["y"], tile_h=v["tile_h"])
+                    _lib.scan_bwd(v["x"], v["a"], v["b"], v["c"], v["dy"], v["dx"], v["da"], v["db"], v["dc"],
+                                  tile_h=v["tile_h"])
+                    self.kernel_launches += 2
                 done = torch.cuda.Event()
                 done.record(self.s_k)
                 computed[k] = done
