@@ -624,6 +624,52 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     fp.h_last = h_last;
 
     const int nin = c != nullptr ? 4 : 3;
+    const bool has_c = c != nullptr, save_h = h_saved != nullptr;
+
+    // Forward that also stores fp32 h (6 of its 14 bytes per element are writes): four adjacent strips per
+    // CTA on 512-byte-wide tiles, under the same conditions as the four-strip backward.  The plain forward
+    // (20 % writes) is at the copy rate with one warp per CTA and stays there.
+    bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W &&
+                (save_h || env_int("QSSM_FWD_TILE4", 0) != 0);
+    if (wide) {
+        const long long groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
+        const long long rounds = (groups + sm_count() - 1) / sm_count();
+        if ((double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
+        if (wide) {
+            const int box = WIDE_W * chans;
+            if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+            if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+            if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+            if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+            if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, box, TB, tma))) return rc;
+            if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, box, TB, tma))) return rc;
+            const long long ctas = (groups + rounds - 1) / rounds;  // equal rounds, at most one CTA per SM
+            const int stage4 = nin * TB * box * es;
+            const int outbuf4 = TB * box * eo + (save_h ? TB * box * 4 : 0);
+            const int n_out4 = env_int("QSSM_NOUT", 2) == 3 ? 3 : 2;
+            fp.g.n_out = n_out4;
+            // measured (bf16, h stored): 3 stages 0.559 ms on the cfg1 shape and 4.72 ms on cfg4, 4 stages
+            // 0.613 / 4.95 ms, 2 stages 0.669 / 4.98 ms; two or three staging tiles make no difference
+            fp.g.n_stages = pick_stages(ctas, stage4, (n_out4 - 1) * outbuf4, n_out4 * outbuf4, 2, 3,
+                                        [](int ns) { return ns - 1; });
+            const int smem4 = fp.g.n_stages * stage4 + n_out4 * outbuf4 + MAX_STAGES * 8;
+            return dispatch(in_dtype, out_dtype, 2, TS, [&](auto tin, auto tout, auto, auto) -> int {
+                using Tin = decltype(tin);
+                using Tout = decltype(tout);
+                if constexpr (sizeof(Tin) == 2) {
+                    const int th = 32 * WIDE_W;
+                    if (has_c && save_h)
+                        return launch(scan_fwd_tile4_kernel<Tin, Tout, true, true>, fp, ctas, smem4, stream, th);
+                    if (has_c) return launch(scan_fwd_tile4_kernel<Tin, Tout, true, false>, fp, ctas, smem4, stream, th);
+                    if (save_h) return launch(scan_fwd_tile4_kernel<Tin, Tout, false, true>, fp, ctas, smem4, stream, th);
+                    return launch(scan_fwd_tile4_kernel<Tin, Tout, false, false>, fp, ctas, smem4, stream, th);
+                } else {
+                    return QSSM_E_DTYPE;
+                }
+            });
+        }
+    }
+
     const int stage = nin * TB * chans * es;
     const int outbuf = TB * chans * eo + (h_saved != nullptr ? TB * chans * 4 : 0);
     int n_out = env_int("QSSM_NOUT", 3);
@@ -633,7 +679,6 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     fp.g.n_stages = pick_stages(pl.grid, stage, (n_out - 1) * outbuf, n_out * outbuf, 2, 8,
                                 [](int ns) { return ns - 1; });
     const int smem = fp.g.n_stages * stage + n_out * outbuf + MAX_STAGES * 8;
-    const bool has_c = c != nullptr, save_h = h_saved != nullptr;
 
     return dispatch(in_dtype, out_dtype, pl.V, pl.TB, [&](auto tin, auto tout, auto v, auto tb) -> int {
         using Tin = decltype(tin);

@@ -473,8 +473,6 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
 // reaches 6.46 TB/s).  One ring of stages and one mbarrier per stage for the whole CTA; thread 0
 // issues every copy; one __syncthreads per tile orders "four strips written" before the store.
 // ---------------------------------------------------------------------------------------------
-constexpr int WIDE_W = 4;
-
 template <typename Tin, typename Tdy, bool SAVED_H>
 __global__ void __launch_bounds__(32 * WIDE_W) scan_bwd_tile4_kernel(const __grid_constant__ BwdParams p) {
     constexpr int W = WIDE_W;

@@ -9,17 +9,20 @@ namespace qssm {
 // ---------------------------------------------------------------------------------------------
 // forward:  y = c*h (HAS_C) or y = h; optional fp32 h, optional tile boundary states
 // ---------------------------------------------------------------------------------------------
-template <typename Tin, typename Tout, int V, bool HAS_C, bool SAVE_H, bool FULL>
+// Tiles have rows of STRIDE lane-vectors and this warp starts at column `col` of a row (32 and 0 when
+// the tile belongs to the warp alone).
+template <typename Tin, typename Tout, int V, bool HAS_C, bool SAVE_H, bool FULL, int STRIDE = 32>
 __device__ __forceinline__ void fwd_batch(const unsigned char* sx, const unsigned char* sa, const unsigned char* sb,
                                           const unsigned char* sc, unsigned char* oy, unsigned char* oh, int lane,
-                                          int nrows, float (&h)[V]) {
+                                          int nrows, float (&h)[V], int col = 0) {
     Vec<Tin, V> xw[TS], aw[TS], bw[TS], cw[HAS_C ? TS : 1];
+    const int at = col + lane;
 #pragma unroll
     for (int r = 0; r < TS; ++r) {
-        xw[r] = tile_raw<Tin, V>(sx, r, lane);
-        aw[r] = tile_raw<Tin, V>(sa, r, lane);
-        bw[r] = tile_raw<Tin, V>(sb, r, lane);
-        if (HAS_C) cw[r] = tile_raw<Tin, V>(sc, r, lane);
+        xw[r] = reinterpret_cast<const Vec<Tin, V>*>(sx)[r * STRIDE + at];
+        aw[r] = reinterpret_cast<const Vec<Tin, V>*>(sa)[r * STRIDE + at];
+        bw[r] = reinterpret_cast<const Vec<Tin, V>*>(sb)[r * STRIDE + at];
+        if (HAS_C) cw[r] = reinterpret_cast<const Vec<Tin, V>*>(sc)[r * STRIDE + at];
     }
     Vec<Tout, V> yw[TS];
     Vec<float, V> hw[SAVE_H ? TS : 1];
@@ -47,8 +50,8 @@ __device__ __forceinline__ void fwd_batch(const unsigned char* sx, const unsigne
     }
 #pragma unroll
     for (int r = 0; r < TS; ++r) {
-        tile_put<Tout, V>(oy, r, lane, yw[r]);
-        if (SAVE_H) tile_put<float, V>(oh, r, lane, hw[r]);
+        reinterpret_cast<Vec<Tout, V>*>(oy)[r * STRIDE + at] = yw[r];
+        if (SAVE_H) reinterpret_cast<Vec<float, V>*>(oh)[r * STRIDE + at] = hw[r];
     }
 }
 
@@ -210,6 +213,161 @@ __global__ void __launch_bounds__(32) scan_fwd_kernel(const __grid_constant__ Fw
 
     if (tma && lane == 0) tma_wait_all();
     if (!ok && lane == 0) report(g.status, QSSM_S_TMA_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward on shared 4-strip tiles (16-bit storage, D > 192, fp32 h stored): a CTA of W = 4 warps scans
+// four adjacent channel strips of one batch entry and time range as ONE tile - one bulk copy of 16 rows
+// x 512 bytes per input tensor, y and h staged 512 / 1024 bytes wide and stored with one bulk copy each.
+// With fp32 h the forward writes 6 of its 14 bytes per element, and like the backward it gains from
+// wider copies (B200, cfg1 shape, checkpoint=False: 5.61 TB/s with one warp per CTA, 6.72 TB/s here;
+// the plain forward, 20 % writes, is at the copy rate with one warp per CTA and 6 % slower here).
+// Thread 0 issues every copy.  Per tile: all warps write their columns of the staging tile, one
+// __syncthreads, thread 0 stores.  Before that barrier thread 0 has waited until the store that last
+// read the NEXT staging tile is done, so the warps may write it right after the barrier.
+// ---------------------------------------------------------------------------------------------
+constexpr int WIDE_W = 4;
+
+template <typename Tin, typename Tout, bool HAS_C, bool SAVE_H>
+__global__ void __launch_bounds__(32 * WIDE_W) scan_fwd_tile4_kernel(const __grid_constant__ FwdParams p) {
+    constexpr int W = WIDE_W;
+    constexpr int V = 2;
+    constexpr int TB = TS;
+    constexpr int DT = 32 * V;
+    constexpr int LANES = 32 * W;  // lane-vectors per tile row
+    constexpr int NIN = HAS_C ? 4 : 3;
+    constexpr int IN_TILE = TB * LANES * V * (int)sizeof(Tin);
+    constexpr int OUT_TILE = TB * LANES * V * (int)sizeof(Tout);
+    constexpr int HS_TILE = SAVE_H ? TB * LANES * V * 4 : 0;
+    constexpr int STAGE = NIN * IN_TILE;
+    constexpr int OUTBUF = OUT_TILE + HS_TILE;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_fail;
+    const Geom& g = p.g;
+    const int NS = g.n_stages;
+    const int NOUT = g.n_out;  // 2 or 3
+    unsigned char* const outbuf = smem + (size_t)NS * STAGE;
+    const uint32_t bars = smem_u32(outbuf + (size_t)NOUT * OUTBUF);
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const bool ld_hint = (g.l2_hint & 1) != 0, st_hint = (g.l2_hint & 2) != 0;
+    const uint64_t pol = l2_policy_evict_first();
+
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        for (int s = 0; s < NS; ++s) mbar_init(bars + 8 * s, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    const int n_dgroups = (g.n_dtiles + W - 1) / W;
+    const long long n_groups = g.B * g.n_seg * n_dgroups;
+    const long long tiles_per_b = (g.L + TS - 1) / TS;
+    RingPos pf{0, 0}, cur{0, 0};
+    int oslot = 0;
+    bool failed = false;
+    for (long long gid = blockIdx.x; gid < n_groups && !failed; gid += gridDim.x) {
+        const long long dgroup = gid % n_dgroups;
+        const long long rest = gid / n_dgroups;
+        const int seg = (int)(rest % g.n_seg);
+        const long long b = rest / g.n_seg;
+        const long long d0 = (dgroup * W + warp) * DT;
+        const long long t_begin = (long long)seg * g.seg_rows;
+        long long t_end = t_begin + g.seg_rows;
+        if (t_end > g.L) t_end = g.L;
+        const int n_tiles = t_end > t_begin ? (int)((t_end - t_begin + TB - 1) / TB) : 0;
+        const long long d_lane = d0 + (long long)lane * V;
+
+        float h[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) h[i] = 0.f;
+        if (p.h_in != nullptr) {
+            const float* src = p.h_in + (b * g.n_seg + seg) * g.D;
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                if (d_lane + i < g.D) h[i] = src[d_lane + i];
+        }
+        float* th_dst = nullptr;
+        if (p.tile_h != nullptr) th_dst = p.tile_h + (b * tiles_per_b + t_begin / TS) * g.D + d_lane;
+
+        const int c0 = (int)(dgroup * W * DT), c2 = (int)b;
+        int pf_row = (int)t_begin;
+        int pf_left = n_tiles;
+        auto issue = [&]() {  // thread 0 only; the stage was read by all warps before the last barrier
+            const uint32_t st = smem_base + pf.s * STAGE;
+            const uint32_t bar = bars + 8 * pf.s;
+            fence_proxy_async();
+            mbar_expect_tx(bar, STAGE);
+            tma_ld(st + 0 * IN_TILE, &p.x.map, bar, c0, pf_row, c2, ld_hint, pol);
+            tma_ld(st + 1 * IN_TILE, &p.a.map, bar, c0, pf_row, c2, ld_hint, pol);
+            tma_ld(st + 2 * IN_TILE, &p.b.map, bar, c0, pf_row, c2, ld_hint, pol);
+            if (HAS_C) tma_ld(st + 3 * IN_TILE, &p.c.map, bar, c0, pf_row, c2, ld_hint, pol);
+            pf.advance(NS);
+            pf_row += TB;
+            --pf_left;
+        };
+        if (threadIdx.x == 0) {
+            for (int k = 0; k < NS - 1 && pf_left > 0; ++k) issue();
+        }
+
+        long long t0 = t_begin;
+        for (int j = 0; j < n_tiles; ++j, t0 += TB) {
+            const unsigned char* st = smem + cur.s * STAGE;
+            unsigned char* ob = outbuf + oslot * OUTBUF;
+            if (++oslot == NOUT) oslot = 0;
+            const int nrows = (int)((t_end - t0) < TB ? (t_end - t0) : TB);
+            if (threadIdx.x == 0 && pf_left > 0) issue();
+            bool ok = mbar_wait_bounded(bars + 8 * cur.s, cur.phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) s_fail = 1;
+            } else {
+                if (th_dst != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i)
+                        if (d_lane + i < g.D) th_dst[i] = h[i];
+                    th_dst += g.D;
+                }
+                if (nrows >= TS)
+                    fwd_batch<Tin, Tout, V, HAS_C, SAVE_H, true, LANES>(st, st + IN_TILE, st + 2 * IN_TILE,
+                                                                        st + 3 * IN_TILE, ob, ob + OUT_TILE, lane, TS, h,
+                                                                        warp * 32);
+                else
+                    fwd_batch<Tin, Tout, V, HAS_C, SAVE_H, false, LANES>(st, st + IN_TILE, st + 2 * IN_TILE,
+                                                                         st + 3 * IN_TILE, ob, ob + OUT_TILE, lane,
+                                                                         nrows, h, warp * 32);
+            }
+            fence_proxy_async();
+            if (threadIdx.x == 0) {  // the staging tile of the next iteration is free once this returns
+                if (NOUT == 2) tma_wait_read<0>();
+                else tma_wait_read<1>();
+            }
+            __syncthreads();
+            if (s_fail != 0) {
+                failed = true;
+                break;
+            }
+            if (threadIdx.x == 0) {
+                tma_st(&p.y.map, smem_u32(ob), c0, (int)t0, c2, st_hint, pol);
+                if (SAVE_H) tma_st(&p.hs.map, smem_u32(ob + OUT_TILE), c0, (int)t0, c2, st_hint, pol);
+                tma_commit();
+            }
+            cur.advance(NS);
+        }
+        if (failed) break;
+        if (p.h_last != nullptr && seg == g.n_seg - 1) {
+            float* dst = p.h_last + b * g.D;
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                if (d_lane + i < g.D) dst[d_lane + i] = h[i];
+        }
+    }
+    if (threadIdx.x == 0) {
+        tma_wait_all();
+        if (failed) report(g.status, QSSM_S_TMA_TIMEOUT);
+    }
 }
 
 // Before chunk k (processing order) writes its descriptor into slot k mod slots it makes sure the

@@ -384,6 +384,29 @@ def test_every_kernel_variant_gives_the_same_answer(monkeypatch, env):
             assert torch.allclose(got[k].float(), base[k].float(), rtol=2e-2, atol=1e-3), k
 
 
+@pytest.mark.parametrize("shape,dtype,out_dtype", [((8, 200, 4096), torch.bfloat16, None),
+                                                   ((8, 200, 4000), torch.float16, None),
+                                                   ((9, 137, 3784), torch.bfloat16, torch.float32)],
+                         ids=["bf16_full_strips", "fp16_ragged_channels", "bf16_fp32_out_ragged"])
+@pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
+@pytest.mark.parametrize("fwd_tile4", ["0", "1"], ids=["fwd_auto", "fwd_four_strips"])
+def test_four_strip_kernels_match_the_oracle(monkeypatch, shape, dtype, out_dtype, checkpoint, fwd_tile4):
+    """Shapes wide enough for the kernels that give a CTA four adjacent strips (16-bit storage, enough
+    groups of four strips to fill the GPU): a partial last tile in time, a channel count that leaves the
+    last group with fewer than four strips and a partial strip, fp32 y/dy, stored h and recompute.  The
+    forward takes the four-strip kernel by itself only when it stores h; QSSM_FWD_TILE4=1 forces it for
+    the other forwards too.  Narrow kernels on the same input must agree within rounding."""
+    monkeypatch.setenv("QSSM_FWD_TILE4", fwd_tile4)
+    inp = make_inputs(*shape, dtype=dtype, out_dtype=out_dtype, seed=47)
+    ref = _oracle(inp, np.float32)
+    got = _run_scan(inp, checkpoint=checkpoint, out_dtype=out_dtype)
+    _check(got, ref, dtype)
+    monkeypatch.setenv("QSSM_WIDE", "0")
+    narrow = _run_scan(inp, checkpoint=checkpoint, out_dtype=out_dtype)
+    for k in got:
+        assert torch.allclose(got[k].float(), narrow[k].float(), rtol=2e-2, atol=1e-3), k
+
+
 def test_expired_wait_is_reported_and_the_context_survives(monkeypatch):
     """The failure path of the bounded waits, on a healthy GPU: a test hook starts the chunk counter of
     the single-pass kernel past the first chunk of every chain, so nothing ever publishes those chunks;
