@@ -234,6 +234,28 @@ int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k,
                     int64_t n_chan, int64_t upto, int reverse,
                     const float* seed, float* carry, void* stream);
 
+/*
+ * RMS normalisation of the layer input, the step before the projections that feed the scan
+ * (RMSNorm.forward, quick_ssm/layers.py:9-17):
+ *     y[r, :] = x[r, :] * w / sqrt(mean(x[r, :]^2) + eps)          r = 0 .. rows-1
+ * x, y, dy, dx: `rows` rows of H elements of `dtype`, row pitches in elements; w, dw: H floats.
+ * forward : writes y and, if rstd != NULL, rstd[r] = 1/sqrt(mean(x^2)+eps) for the backward.
+ * backward: dx = rstd*(w*dy) - x*rstd^3*mean(x*w*dy),  dw = sum_r dy*x*rstd  (fixed summation
+ *           order, no atomics).  ws: at least qssm_rmsnorm_workspace_bytes(H) bytes of scratch.
+ * Rows need H % 4 == 0 and 16-byte aligned bases and pitches (8 bytes for 16-bit data);
+ * otherwise QSSM_E_STRIDE and nothing is launched.
+ */
+size_t qssm_rmsnorm_workspace_bytes(int64_t H);
+
+int qssm_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd,
+                     int64_t rows, int64_t H, int64_t x_stride, int64_t y_stride,
+                     float eps, int dtype, void* stream);
+
+int qssm_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd,
+                     void* dx, float* dw, void* ws, size_t ws_bytes,
+                     int64_t rows, int64_t H, int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
+                     int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

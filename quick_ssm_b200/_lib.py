@@ -44,6 +44,9 @@ SIGNATURES = {
     "qssm_scan_aggregate_bwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
                                 + [_c_int] * 3 + [_c_vp, _c_vp]),
     "qssm_carry_fold": (_c_int, [_c_vp, _c_vp, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_vp, _c_vp, _c_vp]),
+    "qssm_rmsnorm_workspace_bytes": (_c_sz, [_c_i64]),
+    "qssm_rmsnorm_fwd": (_c_int, [_c_vp] * 4 + [_c_i64] * 4 + [ctypes.c_float, _c_int, _c_vp]),
+    "qssm_rmsnorm_bwd": (_c_int, [_c_vp] * 6 + [_c_vp, _c_sz] + [_c_i64] * 5 + [_c_int, _c_vp]),
 }
 
 _lib = None
@@ -309,3 +312,47 @@ def carry_fold(A, H, upto: int, *, reverse: bool, seed=None) -> torch.Tensor:
                                     1 if reverse else 0, _ptr(seed), _ptr(out), _stream(dev))
     _rc(rc, "qssm_carry_fold")
     return out
+
+
+def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
+    """(rows, H, row pitch in elements) of a tensor whose last axis is contiguous and whose leading
+    axes collapse into one row index."""
+    H = t.shape[-1]
+    if t.dim() == 1:
+        return 1, H, H
+    if t.stride(-1) != 1 and H > 1:
+        raise Unsupported("last axis must be contiguous")
+    flat = t.reshape(-1, H) if t.is_contiguous() else None
+    if flat is None:
+        if t.dim() != 2:
+            raise Unsupported("leading axes do not collapse into rows")
+        return t.shape[0], H, t.stride(0)
+    return flat.shape[0], H, H
+
+
+def rmsnorm_fwd(x, w, y, rstd, eps: float) -> None:
+    """y = x * w / sqrt(mean(x^2, -1) + eps); rstd [rows] fp32 receives 1/sqrt(...) (or None)."""
+    dev = _require_cuda(x, w, y, rstd)
+    rows, H, xs = _rows(x)
+    _, _, ys = _rows(y)
+    with torch.cuda.device(dev):
+        rc = load().qssm_rmsnorm_fwd(_ptr(x), _ptr(w), _ptr(y), _ptr(rstd), rows, H, xs, ys, float(eps),
+                                     dtype_code(x.dtype), _stream(dev))
+    if rc in (-3, -4):
+        raise Unsupported(status_string(rc))
+    _rc(rc, "qssm_rmsnorm_fwd")
+
+
+def rmsnorm_bwd(x, w, dy, rstd, dx, dw) -> None:
+    dev = _require_cuda(x, w, dy, rstd, dx, dw)
+    rows, H, xs = _rows(x)
+    _, _, gs = _rows(dy)
+    _, _, ds = _rows(dx)
+    with torch.cuda.device(dev):
+        nbytes = int(load().qssm_rmsnorm_workspace_bytes(H))
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+        rc = load().qssm_rmsnorm_bwd(_ptr(x), _ptr(w), _ptr(dy), _ptr(rstd), _ptr(dx), _ptr(dw), _ptr(ws), nbytes,
+                                     rows, H, xs, gs, ds, dtype_code(x.dtype), _stream(dev))
+    if rc in (-3, -4):
+        raise Unsupported(status_string(rc))
+    _rc(rc, "qssm_rmsnorm_bwd")

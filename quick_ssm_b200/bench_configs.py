@@ -80,6 +80,34 @@ def run_gates(args):
     print(json.dumps(out), flush=True)
 
 
+def run_norm(args):
+    """The pre-norm of configuration 3 (rows = 16 x 4096, hidden 1024): the normalisation kernels against
+    torch's element-wise chain, forward + backward through autograd, fp32 and bf16 activations."""
+    from .norm import _composed, rms_norm
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, L, H = 16, 4096, 1024
+    out = {"config": "cfg3_norm", "shape": [B, L, H]}
+    for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        g = torch.Generator(device=dev).manual_seed(0)
+        x = torch.randn(B, L, H, device=dev, generator=g).to(dt).requires_grad_()
+        dy = torch.randn(B, L, H, device=dev, generator=g).to(dt)
+        w = (torch.randn(H, device=dev, generator=g) * 0.3 + 1.0).requires_grad_()
+
+        def step(fn):
+            x.grad = None
+            w.grad = None
+            fn(x, w, 1e-5).backward(dy)
+
+        fused = _median_ms(lambda: step(rms_norm), args.steps, args.warmup, torch.cuda.synchronize)
+        composed = _median_ms(lambda: step(_composed), args.steps, args.warmup, torch.cuda.synchronize)
+        s = x.element_size()
+        out[name] = {"fused_ms": round(fused, 4), "torch_ms": round(composed, 4), "speedup": round(composed / fused, 2),
+                     "fused_gbs_of_5s_bytes": B * L * H * 5 * s / (fused * 1e-3) / 1e9}
+    print(json.dumps(out), flush=True)
+
+
 def run_stack(args):
     """Configuration 3: the scan inside a 12-layer SSM stack (projections stay torch GEMMs)."""
     from . import scan_interface
@@ -154,7 +182,7 @@ def run_stack(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates"])
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm"])
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
@@ -167,6 +195,8 @@ def main():
         return run_stack(args)
     if args.config == "cfg3_gates":
         return run_gates(args)
+    if args.config == "cfg3_norm":
+        return run_norm(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -42,6 +42,7 @@
 #include "qssm_bwd.cuh"
 #include "qssm_fwd.cuh"
 #include "qssm_gated.cuh"
+#include "qssm_norm.cuh"
 
 using namespace qssm;
 
@@ -1100,6 +1101,134 @@ int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k,
     carry_fold_kernel<<<(unsigned)((n_chan + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         A, H, n, stride_k, n_chan, upto, reverse, seed, carry);
     return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+// =============================================================================================
+// RMS normalisation
+// =============================================================================================
+namespace {
+
+constexpr int NORM_CTAS_PER_SM = 4;  // upper bound used to size the scratch
+constexpr int NORM_FWD_CHUNKS = 32;  // rows of up to 4096 elements stay in registers in the forward,
+constexpr int NORM_BWD_CHUNKS = 16;  // 2048 in the backward (x, w*dy and the dw sums: three values per element)
+
+int norm_check(const void* a, long long stride, long long H, int es) {
+    const long long align = es == 4 ? 16 : 8;
+    if (reinterpret_cast<uintptr_t>(a) % align != 0 || (stride * es) % align != 0 || stride < H) return QSSM_E_STRIDE;
+    return 0;
+}
+
+// calls f(T{}, Int<NCH>{}) for the element type and the number of 128-element chunks held in registers
+// (0 = rows longer than max_chunks chunks: read twice)
+template <typename F> int norm_dispatch(int dtype, long long H, int max_chunks, F&& f) {
+    auto with_type = [&](auto t) -> int {
+        const long long n = (H + 127) / 128;
+        if (n > max_chunks) return f(t, Int<0>{});
+        if (n <= 1) return f(t, Int<1>{});
+        if (n <= 2) return f(t, Int<2>{});
+        if (n <= 4) return f(t, Int<4>{});
+        if (n <= 8) return f(t, Int<8>{});
+        if (n <= 16) return f(t, Int<16>{});
+        return f(t, Int<32>{});
+    };
+    switch (dtype) {
+        case QSSM_F32: return with_type(float{});
+        case QSSM_F16: return with_type(__half{});
+        case QSSM_BF16: return with_type(__nv_bfloat16{});
+        default: return QSSM_E_DTYPE;
+    }
+}
+
+template <typename K> long long norm_grid(K kernel, long long rows, int smem) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * NORM_WARPS, smem) != cudaSuccess) return 0;
+    if (per_sm > NORM_CTAS_PER_SM) per_sm = NORM_CTAS_PER_SM;
+    long long grid = (long long)per_sm * sm_count();
+    const long long need = (rows + NORM_WARPS - 1) / NORM_WARPS;
+    if (grid > need) grid = need;
+    return grid;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t qssm_rmsnorm_workspace_bytes(int64_t H) {
+    if (H <= 0) return 0;
+    // one partial row of dw per CTA, or per warp when rows are too long for the backward's registers
+    const size_t parts = (size_t)sm_count() * NORM_CTAS_PER_SM * (H > 128 * NORM_BWD_CHUNKS ? NORM_WARPS : 1);
+    return parts * (size_t)H * 4;
+}
+
+int qssm_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, int64_t rows, int64_t H, int64_t x_stride,
+                     int64_t y_stride, float eps, int dtype, void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int es = dtype_size(dtype);
+    if (es == 0) return QSSM_E_DTYPE;
+    if (rows < 0 || H < 0 || H >= (1ll << 30)) return QSSM_E_SHAPE;
+    if (rows == 0 || H == 0) return 0;
+    if (x == nullptr || w == nullptr || y == nullptr) return QSSM_E_NULL;
+    int rc;
+    if (H % 4 != 0) return QSSM_E_STRIDE;
+    if ((rc = norm_check(x, x_stride, H, es)) || (rc = norm_check(y, y_stride, H, es)) || (rc = norm_check(w, H, H, 4)))
+        return rc;
+    NormParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = x; p.w = w; p.y = y; p.rstd = rstd;
+    p.rows = rows; p.x_stride = x_stride; p.y_stride = y_stride; p.H = (int)H; p.eps = eps;
+    return norm_dispatch(dtype, H, NORM_FWD_CHUNKS, [&](auto t, auto nch) -> int {
+        using T = decltype(t);
+        auto kernel = rmsnorm_fwd_kernel<T, decltype(nch)::value>;
+        const long long grid = norm_grid(kernel, rows, 0);
+        if (grid < 1) return QSSM_E_SHAPE;
+        kernel<<<(unsigned)grid, 32 * NORM_WARPS, 0, stream>>>(p);
+        return (int)cudaGetLastError();
+    });
+}
+
+int qssm_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd, void* dx, float* dw, void* ws,
+                     size_t ws_bytes, int64_t rows, int64_t H, int64_t x_stride, int64_t dy_stride, int64_t dx_stride,
+                     int dtype, void* stream_v) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int es = dtype_size(dtype);
+    if (es == 0) return QSSM_E_DTYPE;
+    if (rows < 0 || H < 0 || H >= (1ll << 30)) return QSSM_E_SHAPE;
+    if (H == 0) return 0;
+    if (dw == nullptr) return QSSM_E_NULL;
+    if (rows == 0) return (int)cudaMemsetAsync(dw, 0, (size_t)H * 4, stream);
+    if (x == nullptr || w == nullptr || dy == nullptr || rstd == nullptr || dx == nullptr || ws == nullptr)
+        return QSSM_E_NULL;
+    int rc;
+    if (H % 4 != 0) return QSSM_E_STRIDE;
+    if ((rc = norm_check(x, x_stride, H, es)) || (rc = norm_check(dy, dy_stride, H, es)) ||
+        (rc = norm_check(dx, dx_stride, H, es)) || (rc = norm_check(w, H, H, 4)) || (rc = norm_check(ws, H, H, 4)))
+        return rc;
+    if (ws_bytes < qssm_rmsnorm_workspace_bytes(H)) return QSSM_E_WS;
+    NormParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = x; p.w = w; p.y = dx; p.dy = dy; p.rstd = const_cast<float*>(rstd);
+    p.dw_part = static_cast<float*>(ws);
+    p.rows = rows; p.x_stride = x_stride; p.y_stride = dx_stride; p.dy_stride = dy_stride; p.H = (int)H;
+    return norm_dispatch(dtype, H, NORM_BWD_CHUNKS, [&](auto t, auto nch) -> int {
+        using T = decltype(t);
+        constexpr int NCH = decltype(nch)::value;
+        if constexpr (NCH > NORM_BWD_CHUNKS) {
+            return QSSM_E_SHAPE;  // never dispatched: longer rows take NCH = 0
+        } else {
+            auto kernel = rmsnorm_bwd_kernel<T, NCH>;
+            const int smem = NCH > 0 ? (int)H * 4 : 0;
+            const long long grid = norm_grid(kernel, rows, smem);
+            if (grid < 1) return QSSM_E_SHAPE;
+            kernel<<<(unsigned)grid, 32 * NORM_WARPS, smem, stream>>>(p);
+            const int e = (int)cudaGetLastError();
+            if (e) return e;
+            const long long parts = grid * (NCH > 0 ? 1 : NORM_WARPS);
+            rmsnorm_dw_kernel<<<(unsigned)((H + 31) / 32), 256, 0, stream>>>(p.dw_part, dw, parts, (int)H);
+            return (int)cudaGetLastError();
+        }
+    });
 }
 
 }  // extern "C"

@@ -24,6 +24,17 @@ class RMSNorm(nn.Module):
         return x * (self.weight / rms)
 
 
+class RMSNormFused(RMSNorm):
+    """``RMSNorm`` through the normalisation kernels (``norm.rms_norm``): same parameter, same
+    result up to fp32 rounding, one kernel per direction instead of torch's element-wise chain."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.device.type != "cuda":
+            return super().forward(x)
+        from .norm import rms_norm
+        return rms_norm(x, self.weight, self.eps)
+
+
 class SSM(nn.Module):
     """Pre-norm, five input projections (decay, input, two halves of a SwiGLU output gate, input
     gate), the scan over the state dimension, output projection, residual."""
@@ -65,9 +76,10 @@ class SSM(nn.Module):
 
 
 class SSMFused(SSM):
-    """``SSM`` with the gate activations fused into the scan kernels (``gated.gated_scan``): same
-    parameters, same arguments, same result up to the rounding of the activations; the element-wise
-    kernels between the projections and the scan, and their backward, disappear."""
+    """``SSM`` with the gate activations fused into the scan kernels (``gated.gated_scan``) and the
+    pre-norm done by the normalisation kernels (``norm.rms_norm``): same parameters, same arguments,
+    same result up to the rounding of the activations; the element-wise kernels around the
+    projections, and their backward, disappear."""
 
     def forward(self, x: torch.Tensor, *, block_l: int = 256, checkpoint: bool = True,
                 tile_b: Optional[int] = None, tile_d: Optional[int] = None, backend: str = "auto",
@@ -77,7 +89,11 @@ class SSMFused(SSM):
                                    backend=backend, scan_out_dtype=scan_out_dtype)
         from .gated import gated_scan
         skip = x if self.use_residual else 0
-        u = self.pre_norm(x) if self.use_norm else x
+        if self.use_norm:  # the normalisation kernels on the layer's own weight
+            from .norm import rms_norm
+            u = rms_norm(x, self.pre_norm.weight, self.pre_norm.eps)
+        else:
+            u = x
         if scan_out_dtype is None:
             scan_out_dtype = self.out_proj.weight.dtype
         h = gated_scan(self.A_proj(u), self.B_proj(u), self.C_proj_a(u), self.C_proj_b(u), self.D_proj(u),
@@ -85,4 +101,4 @@ class SSMFused(SSM):
         return self.out_proj(h.to(self.out_proj.weight.dtype)) + skip
 
 
-__all__ = ["SSM", "SSMFused", "RMSNorm"]
+__all__ = ["SSM", "SSMFused", "RMSNorm", "RMSNormFused"]
