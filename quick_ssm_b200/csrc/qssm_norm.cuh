@@ -158,24 +158,32 @@ __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const Norm
         const float r = p.rstd[row];
         float dot = 0.f;
         if (NCH > 0) {
+            // all loads of the row first (they are independent: the whole row is in flight at once), then
+            // the arithmetic; wg holds dy on the way in and w*dy afterwards
             float v[NCH > 0 ? NCH : 1][4], wg[NCH > 0 ? NCH : 1][4];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
                 const int col = (c * 32 + lane) * 4;
                 if (col < H) {
-                    float g[4], w4[4];
                     load4<T>(xr + col, v[c]);
-                    load4<T>(gr + col, g);
-                    load4<float>(p.w + col, w4);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        acc[c][i] = fmaf(g[i] * r, v[c][i], acc[c][i]);
-                        wg[c][i] = w4[i] * g[i];
-                        dot = fmaf(v[c][i], wg[c][i], dot);
-                    }
+                    load4<T>(gr + col, wg[c]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) v[c][i] = wg[c][i] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                const int col = (c * 32 + lane) * 4;
+                if (col < H) {
+                    float w4[4];
+                    load4<float>(p.w + col, w4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[c][i] = fmaf(wg[c][i] * r, v[c][i], acc[c][i]);
+                        wg[c][i] *= w4[i];
+                        dot = fmaf(v[c][i], wg[c][i], dot);
+                    }
                 }
             }
             dot = warp_sum(dot);
