@@ -410,18 +410,22 @@ struct ChainedLayout {
 // 0 = never, 1 = when the time axis would otherwise be segmented, 2 = whenever the shape allows (tests)
 int chained_mode() { return env_int("QSSM_CHAINED", 1); }
 
-// Chunks of 256 rows of 16-bit data (128 of fp32): with about a thousand chunks in flight the three
-// tensors the first pass leaves in L2 for the second one take ~100 MB of the 126 MB L2; measured on
-// B200 the second pass then reads them from L2 (DRAM reads = one pass), with 512 rows it does not.
-ChainedLayout chained_layout(long long B, long long L, long long D, int elem_size) {
+// Chunk length: with about a thousand chunks in flight, the tensors the first pass leaves in L2 for the
+// second one (three of them, 128 bytes per row) have to fit in the 126 MB L2 next to the streaming
+// traffic; shorter chunks mean more look-backs.  Measured on B200, 1 x 2^20 x 2048 fp16: the forward is
+// fastest with 192-224 rows (3.67 ms; 256: 3.81, 160: 3.77, 128: 3.84), the backward with 128 rows and
+// two stages, which lets nine CTAs share an SM (6.83 ms; 256 rows and four stages: 6.93); 512 rows
+// overflow the L2 and the second pass reads HBM again.
+ChainedLayout chained_layout(long long B, long long L, long long D, int elem_size, bool backward) {
     ChainedLayout c;
     c.n_chains = B * ((D + 63) / 64);
-    c.chunk_rows = env_int("QSSM_CHUNK_ROWS", elem_size == 2 ? 256 : 128);
+    c.chunk_rows = env_int("QSSM_CHUNK_ROWS", elem_size == 2 ? (backward ? 128 : 192) : 128);
     if (c.chunk_rows < TS) c.chunk_rows = TS;
     c.chunk_rows = (c.chunk_rows / TS) * TS;
     c.n_chunks = (int)((L + c.chunk_rows - 1) / c.chunk_rows);
     // two warps per scheduler: the two passes make a lone warp per scheduler compute-bound
-    c.grid = env_int("QSSM_CHAINED_GRID", 0) > 0 ? env_int("QSSM_CHAINED_GRID", 0) : 8ll * sm_count();
+    c.grid = env_int("QSSM_CHAINED_GRID", 0) > 0 ? env_int("QSSM_CHAINED_GRID", 0)
+                                                  : (backward && elem_size == 2 ? 9ll : 8ll) * sm_count();
     const long long total = c.n_chains * c.n_chunks;
     if (c.grid > total) c.grid = total;
     if (c.grid < 1) c.grid = 1;
@@ -447,7 +451,9 @@ size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
     // measured crossover: below about 2.75 chains per SM the chained kernels (~182 Gelem/s fwd+bwd on
     // 16-bit data whatever the chain count) beat one warp per chain (168 at 384 chains, 196 at 448)
     if (mode == 1 && 4 * B * ((D + 63) / 64) >= 11 * (long long)sm_count()) return 0;
-    return chained_layout(B, L, D, dtype_size(in_dtype)).bytes;
+    const size_t f = chained_layout(B, L, D, dtype_size(in_dtype), false).bytes;
+    const size_t r = chained_layout(B, L, D, dtype_size(in_dtype), true).bytes;
+    return f > r ? f : r;
 }
 
 unsigned long long lookback_wait_ns() {
@@ -545,7 +551,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
         if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
             tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
             tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo)) {
-            const ChainedLayout lay = chained_layout(B, L, D, es);
+            const ChainedLayout lay = chained_layout(B, L, D, es, false);
             ChainedParams cp;
             memset(&cp, 0, sizeof(cp));
             Geom& g = cp.f.g;
@@ -759,7 +765,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
             tma_ok(dx, B, L, D, g_sb, g_sl, es) && tma_ok(da, B, L, D, g_sb, g_sl, es) &&
             tma_ok(db, B, L, D, g_sb, g_sl, es) && tma_ok(dc, B, L, D, g_sb, g_sl, es) &&
             tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4)) {
-            const ChainedLayout lay = chained_layout(B, L, D, es);
+            const ChainedLayout lay = chained_layout(B, L, D, es, true);
             ChainedBwdParams cp;
             memset(&cp, 0, sizeof(cp));
             Geom& g = cp.f.g;
@@ -770,7 +776,8 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
             g.l2_hint = env_int("QSSM_CHAINED_HINT", 1);
             g.status = status_word;
             g.n_chains = lay.n_chains;
-            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0) : 4;
+            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0)
+                                                                                          : (es == 2 ? 2 : 4);
             const int chans = 64;
             BwdParams& f = cp.f;
             if ((rc = fill_desc(f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
