@@ -13,9 +13,16 @@
 //    into a ring of shared-memory stages (completion on an mbarrier per
 //    stage); the warp scans the current tile out of shared memory, 16 rows at
 //    a time, with fp32 state in registers, writes results back to shared
-//    memory and lane 0 issues the bulk tensor store.  One CTA == one warp, so
-//    no CTA-wide barrier exists anywhere; many small CTAs per SM give the
-//    latency hiding;
+//    memory and lane 0 issues the bulk tensor store.  One CTA == one warp:
+//    many small CTAs per SM give the latency hiding;
+//  * the write-heavy launches on 16-bit data (the backward; the forward that
+//    also stores fp32 h) give four adjacent strips to a CTA of four warps,
+//    which loads and stores them as one 512-byte-wide tile per tensor with
+//    one __syncthreads per tile (scan_bwd_tile4_kernel, scan_fwd_tile4_kernel);
+//  * with very few chains (long sequences of a few thousand channels) the
+//    chained kernels cut every chain into chunks claimed from a ticket
+//    counter and pass the carry between chunks through descriptors in
+//    global memory (decoupled look-back, every wait bounded);
 //  * the carry between tiles of a chain never leaves registers.  When B*D
 //    alone gives too few chains to fill the GPU the time axis is cut into
 //    segments: an aggregate kernel (reads only the tensors the carry depends
@@ -31,7 +38,8 @@
 // QSSM_S_TMA_TIMEOUT in the caller's status word and leaves.
 //
 // Files: qssm_ptx.cuh (PTX wrappers), qssm_tile.cuh (element/tile helpers, parameter blocks),
-// qssm_fwd.cuh, qssm_bwd.cuh, qssm_agg.cuh (kernels), this file (launch planning and the C ABI).
+// qssm_fwd.cuh, qssm_bwd.cuh, qssm_agg.cuh (scan kernels), qssm_gated.cuh (scan with the layer's gate
+// activations fused in), qssm_norm.cuh (the layer's RMS norm), this file (launch planning and the C ABI).
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
