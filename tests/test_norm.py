@@ -51,6 +51,30 @@ def test_oracle_backward_is_the_derivative_of_its_forward():
     assert abs(num - dw[5]) <= 1e-6 * max(1.0, abs(dw[5]))
 
 
+def test_composed_path_and_layer_match_the_oracle_on_cpu():
+    """The torch composition used for row lengths the kernels do not take, and the mirrored layer on
+    CPU tensors, follow the same formula as the oracle (float64)."""
+    from quick_ssm_b200.layers import RMSNorm, RMSNormFused
+    from quick_ssm_b200.norm import _composed, rms_norm
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(3, 5, 30, generator=g, dtype=torch.float64, requires_grad=True)
+    w = (torch.randn(30, generator=g, dtype=torch.float64) * 0.3 + 1.0).requires_grad_()
+    dy = torch.randn(3, 5, 30, generator=g, dtype=torch.float64)
+    y = _composed(x, w, 1e-5)
+    y.backward(dy)
+    ry, _ = no.rmsnorm_forward(x.detach().numpy(), w.detach().numpy(), 1e-5)
+    rdx, rdw = no.rmsnorm_backward(x.detach().numpy(), w.detach().numpy(), dy.numpy(), 1e-5)
+    assert np.abs(y.detach().numpy() - ry).max() <= 1e-12
+    assert np.abs(x.grad.numpy() - rdx).max() <= 1e-12 and np.abs(w.grad.numpy() - rdw).max() <= 1e-11
+    for cls in (RMSNorm, RMSNormFused):  # CPU tensors: both modules are the torch formula
+        m = cls(30, dtype=torch.float64)
+        with torch.no_grad():
+            m.weight.copy_(w)
+        assert np.abs(m(x.detach()).detach().numpy() - ry).max() <= 1e-12
+    with pytest.raises(RuntimeError):
+        rms_norm(x.detach().float(), w.detach().float(), 1e-5)  # the kernel entry point has no CPU path
+
+
 # ------------------------------------------------------------------------------------------------
 # GPU
 # ------------------------------------------------------------------------------------------------
