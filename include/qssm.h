@@ -59,6 +59,20 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int qssm_version(void);
 
+/*
+ * Tuning knobs and the test hook.  No counterpart in the reference; production callers use neither.
+ * Launch-shape choices (strip width "V", tile rows "TB", ring depth "STAGES", "NOUT", "GRID", "WIDE",
+ * "FWD_TILE4", "NO_TMA", "L2HINT", the single-pass kernels "CHAINED", "CHUNK_ROWS", "CHAINED_GRID",
+ * "CHAINED_HINT", "RESIDENT", the limit of bounded waits "WAIT_MS", "DEBUG") take their values from the
+ * environment variables QSSM_<NAME> once, when the library is first used; afterwards only these two
+ * calls change them, process-wide.  No launch reads the environment.  "TEST_SKIP_FIRST_CHUNK" (no
+ * environment form) makes the single-pass kernels skip the first chunk of every chain, so that their
+ * bounded waits expire: the host-side way to exercise the device error path on a healthy GPU.
+ * qssm_tune_set returns 0, or QSSM_E_SHAPE for an unknown name; qssm_tune_reset restores the start-up values.
+ */
+int qssm_tune_set(const char* name, int value);
+void qssm_tune_reset(void);
+
 /* Text for a return value of any entry point or for a QSSM_S_* status code. */
 const char* qssm_status_string(int code);
 
@@ -125,13 +139,19 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
  * Limits and rules
  *   - the scratch the shape needs, 3 * B * n_seg * D * 4 bytes with n_seg = the `n_seg` argument or,
  *     for 0, qssm_auto_segments(), must fit: otherwise QSSM_E_STATIC_WS is returned and nothing
- *     is launched (the call never silently runs unsegmented);
+ *     is launched (the call never silently runs unsegmented).  With n_seg = 0 and no h_saved the
+ *     library may run a few-chain, long-sequence shape with its single-pass kernels; their ticket
+ *     counter and chunk descriptors (qssm_workspace_bytes) then live in the array as well, must fit
+ *     too, and are zeroed by a memset on `stream` at the start of the call;
+ *   - n_seg < 0 ("aggregates already in ws") is refused with QSSM_E_SHAPE: no aggregate entry point
+ *     writes the built-in array, so there is nothing to reuse;
  *   - the first call on each device looks up the device address of the array (a short host-side
  *     runtime query, done with that device current); make that first call outside any stream
  *     capture;
  *   - all calls on one GPU share the one array and it keeps whatever the previous call left in
- *     it.  Nothing in it has to start at zero: every entry is written by the aggregate and carry
- *     kernels of a call before the scan kernel of the same call reads it.  Two calls whose
+ *     it.  The segment path needs nothing in it to start at zero (every entry is written by the
+ *     aggregate and carry kernels of a call before the scan kernel of the same call reads it); the
+ *     single-pass path clears what it needs itself, as said above.  Two calls whose
  *     kernels can overlap on the GPU (different streams, no ordering between them) race on it:
  *     order them, or use qssm_scan_fwd with separate `ws` buffers.
  */

@@ -26,6 +26,8 @@ _c_i64, _c_int, _c_vp, _c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ct
 SIGNATURES = {
     "qssm_version": (_c_int, []),
     "qssm_status_string": (ctypes.c_char_p, [_c_int]),
+    "qssm_tune_set": (_c_int, [ctypes.c_char_p, _c_int]),
+    "qssm_tune_reset": (None, []),
     "qssm_tile_rows": (_c_int, []),
     "qssm_workspace_bytes": (_c_sz, [_c_i64, _c_i64, _c_i64, _c_int]),
     "qssm_auto_segments": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int]),
@@ -70,6 +72,17 @@ def load() -> ctypes.CDLL:
                     fn.argtypes = args
                 _lib = lib
     return _lib
+
+
+def tune_set(name: str, value: int) -> None:
+    """Set one launch-shape knob of the library (measurement scripts and tests only)."""
+    if load().qssm_tune_set(name.encode(), int(value)) != 0:
+        raise KeyError(f"unknown qssm tuning knob '{name}'")
+
+
+def tune_reset() -> None:
+    """Put every knob back to its start-up value (the QSSM_<NAME> environment variables, read once)."""
+    load().qssm_tune_reset()
 
 
 def status_string(code: int) -> str:

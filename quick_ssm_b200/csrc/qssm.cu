@@ -40,11 +40,14 @@
 // Files: qssm_ptx.cuh (PTX wrappers), qssm_tile.cuh (element/tile helpers, parameter blocks),
 // qssm_fwd.cuh, qssm_bwd.cuh, qssm_agg.cuh (scan kernels), qssm_gated.cuh (scan with the layer's gate
 // activations fused in), qssm_norm.cuh (the layer's RMS norm), this file (launch planning and the C ABI).
+#include <limits.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <type_traits>
+#include <unordered_map>
 
 #include "qssm_agg.cuh"
 #include "qssm_bwd.cuh"
@@ -99,9 +102,44 @@ bool tma_ok(const void* ptr, long long B, long long L, long long D, long long sb
     return true;
 }
 
-int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+// ---------------------------------------------------------------------------------------------
+// Tuning knobs.  Production callers set none of them.  Each knob is read from the environment
+// variable QSSM_<NAME> once, when the library is first used, and can be changed afterwards only
+// through qssm_tune_set (measurement scripts and tests); launches never call getenv.
+// TEST_SKIP_FIRST_CHUNK is a test hook and has no environment form.
+// ---------------------------------------------------------------------------------------------
+enum Knob {
+    K_GRID, K_V, K_TB, K_STAGES, K_NOUT, K_WIDE, K_FWD_TILE4, K_NO_TMA, K_L2HINT, K_CHAINED, K_CHUNK_ROWS,
+    K_CHAINED_GRID, K_CHAINED_HINT, K_WAIT_MS, K_DEBUG, K_RESIDENT, K_TEST_SKIP_FIRST_CHUNK, K_COUNT
+};
+const char* const kKnobNames[K_COUNT] = {"GRID", "V", "TB", "STAGES", "NOUT", "WIDE", "FWD_TILE4", "NO_TMA", "L2HINT",
+                                         "CHAINED", "CHUNK_ROWS", "CHAINED_GRID", "CHAINED_HINT", "WAIT_MS", "DEBUG",
+                                         "RESIDENT", "TEST_SKIP_FIRST_CHUNK"};
+constexpr int KNOB_UNSET = INT_MIN;
+
+struct Knobs {
+    int now[K_COUNT];    // current values (KNOB_UNSET = use the call site's default)
+    int start[K_COUNT];  // values taken from the environment at first use
+    Knobs() {
+        for (int k = 0; k < K_COUNT; ++k) {
+            start[k] = KNOB_UNSET;
+            if (k != K_TEST_SKIP_FIRST_CHUNK) {
+                char name[64];
+                snprintf(name, sizeof(name), "QSSM_%s", kKnobNames[k]);
+                const char* v = getenv(name);
+                if (v != nullptr && *v != '\0') start[k] = atoi(v);
+            }
+            now[k] = start[k];
+        }
+    }
+};
+Knobs& knobs() {
+    static Knobs k;
+    return k;
+}
+inline int knob(Knob k, int dflt) {
+    const int v = __atomic_load_n(&knobs().now[k], __ATOMIC_RELAXED);
+    return v == KNOB_UNSET ? dflt : v;
 }
 
 // dims (D, rows, B); box (box_d, box_rows, 1)
@@ -130,7 +168,7 @@ int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long ro
     CUresult r = enc(&td.map, tm_dtype(dt), 3, const_cast<void*>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS && env_int("QSSM_DEBUG", 0) != 0)
+    if (r != CUDA_SUCCESS && knob(K_DEBUG, 0) != 0)
         fprintf(stderr,
                 "qssm: cuTensorMapEncodeTiled failed (%d): ptr=%p dt=%d dims=(%llu,%llu,%llu) strides=(%llu,%llu) "
                 "box=(%u,%u,%u)\n",
@@ -140,13 +178,25 @@ int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long ro
     return r == CUDA_SUCCESS ? 0 : QSSM_E_STRIDE;
 }
 
+constexpr int MAX_DEVICES = 64;
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+    return dev;
+}
+
+// SM count of the current device (looked up once per device ordinal).
 int sm_count() {
-    static int n = []() {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-        return v;
-    }();
+    static int cached[MAX_DEVICES];
+    const int dev = current_device();
+    int n = __atomic_load_n(&cached[dev], __ATOMIC_RELAXED);
+    if (n <= 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n = v;
+        __atomic_store_n(&cached[dev], n, __ATOMIC_RELAXED);
+    }
     return n;
 }
 
@@ -165,7 +215,7 @@ struct Plan {
 // than that therefore run them in equal rounds on a grid near the sweet spot; a launch is cut
 // into rounds only when every round still fills the GPU.
 long long concurrent_chains(long long chains, bool write_heavy) {
-    const long long forced_grid = env_int("QSSM_GRID", 0);
+    const long long forced_grid = knob(K_GRID, 0);
     if (forced_grid > 0) return forced_grid < chains ? forced_grid : chains;
     const double target = write_heavy ? 3.5 * sm_count() : 4.0 * sm_count();
     long long rounds = (long long)((double)chains / target + (write_heavy ? 0.2 : 0.3));
@@ -179,7 +229,7 @@ long long concurrent_chains(long long chains, bool write_heavy) {
 // forward + backward: all chains at once 2.12 ms with bf16 and 2.89 ms with fp32 projection outputs,
 // two rounds of 512 chains 2.73 / 3.16 ms.
 long long concurrent_chains_gated(long long chains) {
-    const long long forced_grid = env_int("QSSM_GRID", 0);
+    const long long forced_grid = knob(K_GRID, 0);
     if (forced_grid > 0) return forced_grid < chains ? forced_grid : chains;
     const long long cap = 8ll * sm_count();
     const long long rounds = (chains + cap - 1) / cap;
@@ -191,14 +241,14 @@ long long concurrent_chains_gated(long long chains) {
 // that would leave half of a wide strip empty, or for launches with too few chains to give
 // every SM two warps even after the time axis has been segmented.
 int pick_v(long long B, long long D, int n_seg) {
-    const int forced = env_int("QSSM_V", 0);
+    const int forced = knob(K_V, 0);
     if (forced == 1 || forced == 2) return forced;
     if (D <= 32) return 1;
     const long long chains_v2 = B * ((D + 63) / 64) * (n_seg < 1 ? 1 : n_seg);
     return chains_v2 >= 2ll * sm_count() ? 2 : 1;
 }
 int pick_tb() {
-    const int forced = env_int("QSSM_TB", 0);
+    const int forced = knob(K_TB, 0);
     return forced == 16 || forced == 32 ? forced : 16;
 }
 
@@ -236,7 +286,7 @@ size_t ws_bytes_for(long long B, long long D, int n_seg) {
 template <typename F>
 int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_bytes, int lo, int hi, F prefetch,
                 long long total_budget = 15ll << 20) {
-    const int forced = env_int("QSSM_STAGES", 0);
+    const int forced = knob(K_STAGES, 0);
     if (forced >= lo && forced <= MAX_STAGES &&
         (long long)forced * stage_bytes + fixed_bytes + MAX_STAGES * 8 <= 227 * 1024)
         return forced;
@@ -260,7 +310,7 @@ int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* s
     seg_rows = ((seg_rows + 31) / 32) * 32;  // whole tiles for either tile height
     n_seg = (int)((L + seg_rows - 1) / seg_rows);
     pl.V = pick_v(B, D, n_seg);
-    if (force_v > 0 && env_int("QSSM_V", 0) == 0) pl.V = force_v;
+    if (force_v > 0 && knob(K_V, 0) == 0) pl.V = force_v;
     pl.TB = pick_tb();
     const int chans = 32 * pl.V;
     Geom& g = pl.g;
@@ -270,7 +320,7 @@ int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* s
     g.seg_rows = (int)seg_rows;
     g.status = status;
     g.use_tma = 1;
-    g.l2_hint = env_int("QSSM_L2HINT", 0);
+    g.l2_hint = knob(K_L2HINT, 0);
     g.n_stages = 2;
     pl.chains = B * n_seg * g.n_dtiles;
     g.n_chains = pl.chains;
@@ -278,13 +328,40 @@ int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* s
     return 0;
 }
 
-template <typename K, typename P>
-int launch(K kernel, const P& params, long long grid, int smem_bytes, cudaStream_t stream, int threads = 32) {
+// Per kernel instantiation and device: the largest dynamic shared-memory size the function has been
+// opted into, and how many of its CTAs fit on an SM at a given size.  Both are asked of the runtime
+// once, not on every launch.
+struct KernelCache {
+    std::mutex mu;
+    std::unordered_map<unsigned long long, int> smem_set;   // (kernel, device) -> bytes
+    std::unordered_map<unsigned long long, int> per_sm;     // (kernel, device, smem, threads) -> CTAs per SM
+};
+KernelCache& kernel_cache() {
+    static KernelCache c;
+    return c;
+}
+inline unsigned long long kernel_key(const void* fn, int dev) {
+    return (unsigned long long)reinterpret_cast<uintptr_t>(fn) * 64ull + (unsigned long long)dev;
+}
+
+template <typename K> int ensure_smem(K kernel, int smem_bytes) {
+    KernelCache& kc = kernel_cache();
+    const unsigned long long key = kernel_key(reinterpret_cast<const void*>(kernel), current_device());
+    std::lock_guard<std::mutex> lock(kc.mu);
+    auto it = kc.smem_set.find(key);
+    if (it != kc.smem_set.end() && it->second >= smem_bytes) return 0;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return (int)e;
+    kc.smem_set[key] = smem_bytes;
+    return 0;
+}
+
+template <typename K, typename P>
+int launch(K kernel, const P& params, long long grid, int smem_bytes, cudaStream_t stream, int threads = 32) {
+    const int rc = ensure_smem(kernel, smem_bytes);
+    if (rc) return rc;
     kernel<<<(unsigned)grid, threads, smem_bytes, stream>>>(params);
-    e = cudaGetLastError();
-    return (int)e;
+    return (int)cudaGetLastError();
 }
 
 int check_common(long long B, long long L, long long D, int in_dtype, int out_dtype) {
@@ -341,7 +418,7 @@ int run_aggregate(bool reverse, const void* t0, const void* t1, const void* t2, 
     const int chans = 32 * pl.V, TB = pl.TB;
     bool tma = tma_ok(t0, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
                tma_ok(t1, g.B, g.L, g.D, sb, sl, dtype_size(in_dtype)) &&
-               tma_ok(t2, g.B, g.L, g.D, sb2, sl2, dtype_size(dt2)) && env_int("QSSM_NO_TMA", 0) == 0;
+               tma_ok(t2, g.B, g.L, g.D, sb2, sl2, dtype_size(dt2)) && knob(K_NO_TMA, 0) == 0;
     ap.g.use_tma = tma ? 1 : 0;
     int rc;
     if ((rc = fill_desc(ap.t0, t0, in_dtype, g.B, g.L, g.D, sb, sl, chans, TB, tma))) return rc;
@@ -384,7 +461,6 @@ int resolve_segments(int n_seg_req, long long B, long long L, long long D, int i
 // ---------------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_static_ws[QSSM_STATIC_WS_BYTES];
 
-constexpr int MAX_DEVICES = 64;
 void* g_static_ws_addr[MAX_DEVICES];  // device address of g_static_ws on each device, once resolved
 
 // Device address of the built-in scratch on the current device.  `g_static_ws` in host code is only
@@ -416,7 +492,7 @@ struct ChainedLayout {
 };
 
 // 0 = never, 1 = when the time axis would otherwise be segmented, 2 = whenever the shape allows (tests)
-int chained_mode() { return env_int("QSSM_CHAINED", 1); }
+int chained_mode() { return knob(K_CHAINED, 1); }
 
 // Chunk length: with about a thousand chunks in flight, the tensors the first pass leaves in L2 for the
 // second one (three of them, 128 bytes per row) have to fit in the 126 MB L2 next to the streaming
@@ -427,12 +503,12 @@ int chained_mode() { return env_int("QSSM_CHAINED", 1); }
 ChainedLayout chained_layout(long long B, long long L, long long D, int elem_size, bool backward) {
     ChainedLayout c;
     c.n_chains = B * ((D + 63) / 64);
-    c.chunk_rows = env_int("QSSM_CHUNK_ROWS", elem_size == 2 ? (backward ? 128 : 192) : 128);
+    c.chunk_rows = knob(K_CHUNK_ROWS, elem_size == 2 ? (backward ? 128 : 192) : 128);
     if (c.chunk_rows < TS) c.chunk_rows = TS;
     c.chunk_rows = (c.chunk_rows / TS) * TS;
     c.n_chunks = (int)((L + c.chunk_rows - 1) / c.chunk_rows);
     // two warps per scheduler: the two passes make a lone warp per scheduler compute-bound
-    c.grid = env_int("QSSM_CHAINED_GRID", 0) > 0 ? env_int("QSSM_CHAINED_GRID", 0)
+    c.grid = knob(K_CHAINED_GRID, 0) > 0 ? knob(K_CHAINED_GRID, 0)
                                                   : (backward && elem_size == 2 ? 9ll : 8ll) * sm_count();
     const long long total = c.n_chains * c.n_chunks;
     if (c.grid > total) c.grid = total;
@@ -465,7 +541,7 @@ size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
 }
 
 unsigned long long lookback_wait_ns() {
-    const int ms = env_int("QSSM_WAIT_MS", 2000);
+    const int ms = knob(K_WAIT_MS, 2000);
     return (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
 }
 
@@ -475,11 +551,9 @@ unsigned long long lookback_wait_ns() {
 int prepare_chained_ws(void* ws, const ChainedLayout& lay, cudaStream_t stream) {
     cudaError_t e = cudaMemsetAsync(ws, 0, lay.zero_bytes, stream);
     if (e != cudaSuccess) return (int)e;
-    if (env_int("QSSM_TEST_SKIP_FIRST_CHUNK", 0) != 0) {
+    if (knob(K_TEST_SKIP_FIRST_CHUNK, 0) != 0) {
         static unsigned int start[MAX_DEVICES];
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev < 0 || dev >= MAX_DEVICES) return QSSM_E_SHAPE;
+        const int dev = current_device();
         start[dev] = (unsigned int)lay.n_chains;
         e = cudaMemcpyAsync(ws, &start[dev], sizeof(unsigned int), cudaMemcpyHostToDevice, stream);
         if (e != cudaSuccess) return (int)e;
@@ -488,9 +562,22 @@ int prepare_chained_ws(void* ws, const ChainedLayout& lay, cudaStream_t stream) 
 }
 
 template <typename K> long long resident_ctas(K kernel, int threads, int smem) {
+    if (ensure_smem(kernel, smem) != 0) return 0;
+    KernelCache& kc = kernel_cache();
+    const unsigned long long key =
+        (kernel_key(reinterpret_cast<const void*>(kernel), current_device()) * 1048576ull + (unsigned)smem) * 2048ull +
+        (unsigned)threads;
     int per_sm = 0;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) return 0;
+    {
+        std::lock_guard<std::mutex> lock(kc.mu);
+        auto it = kc.per_sm.find(key);
+        if (it != kc.per_sm.end()) per_sm = it->second;
+    }
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) return 0;
+        std::lock_guard<std::mutex> lock(kc.mu);
+        kc.per_sm[key] = per_sm;
+    }
     return (long long)per_sm * sm_count();
 }
 
@@ -501,7 +588,23 @@ template <typename K> long long resident_ctas(K kernel, int threads, int smem) {
 // =============================================================================================
 extern "C" {
 
-int qssm_version(void) { return 100; }
+int qssm_version(void) { return 200; }
+
+int qssm_tune_set(const char* name, int value) {
+    if (name == nullptr) return QSSM_E_NULL;
+    if (strncmp(name, "QSSM_", 5) == 0) name += 5;
+    for (int k = 0; k < K_COUNT; ++k)
+        if (strcmp(name, kKnobNames[k]) == 0) {
+            __atomic_store_n(&knobs().now[k], value, __ATOMIC_RELAXED);
+            return 0;
+        }
+    return QSSM_E_SHAPE;
+}
+
+void qssm_tune_reset(void) {
+    Knobs& k = knobs();
+    for (int i = 0; i < K_COUNT; ++i) __atomic_store_n(&k.now[i], k.start[i], __ATOMIC_RELAXED);
+}
 
 int qssm_tile_rows(void) { return TS; }
 
@@ -553,7 +656,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     if ((rc = check_strides(L, D, out_stride_b, out_stride_l))) return rc;
 
     // Few chains, long sequence: single-pass chained kernel instead of aggregate + carry + scan.
-    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && env_int("QSSM_NO_TMA", 0) == 0) {
+    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
         const size_t need = chained_ws_bytes(B, L, D, in_dtype);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
@@ -568,11 +671,11 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
             g.n_seg = 1;
             g.seg_rows = 0;
             g.use_tma = 1;
-            g.l2_hint = env_int("QSSM_CHAINED_HINT", 1);
+            g.l2_hint = knob(K_CHAINED_HINT, 1);
             g.status = status_word;
             g.n_chains = lay.n_chains;
             g.n_out = 3;
-            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0) : 3;
+            g.n_stages = knob(K_STAGES, 0) >= 2 && knob(K_STAGES, 0) <= 8 ? knob(K_STAGES, 0) : 3;
             const int chans = 64;
             if ((rc = fill_desc(cp.f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
             if ((rc = fill_desc(cp.f.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
@@ -637,17 +740,11 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
     const int chans = 32 * pl.V, TB = pl.TB;
     const long long hs_sb = L * D, hs_sl = D;
-    bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+    bool tma = knob(K_NO_TMA, 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo) &&
                tma_ok(h_saved, B, L, D, hs_sb, hs_sl, 4);
     fp.g.use_tma = tma ? 1 : 0;
-    if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, chans, TB, tma))) return rc;
     fp.tile_h = tile_h;
     fp.h_in = seeds;
     fp.h_last = h_last;
@@ -658,24 +755,30 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     // Forward that also stores fp32 h (6 of its 14 bytes per element are writes): four adjacent strips per
     // CTA on 512-byte-wide tiles, under the same conditions as the four-strip backward.  The plain forward
     // (20 % writes) is at the copy rate with one warp per CTA and stays there.
-    bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W &&
-                (save_h || env_int("QSSM_FWD_TILE4", 0) != 0);
+    bool wide = tma && knob(K_WIDE, 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W &&
+                (save_h || knob(K_FWD_TILE4, 0) != 0);
+    const long long groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
+    const long long rounds = (groups + sm_count() - 1) / sm_count();
+    if (wide && (double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
+
+    // tensor maps, encoded once with the box of the kernel that will run
+    {
+        const int box = wide ? WIDE_W * chans : chans;
+        if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, box, TB, tma))) return rc;
+        if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, box, TB, tma))) return rc;
+    }
+
     if (wide) {
-        const long long groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
-        const long long rounds = (groups + sm_count() - 1) / sm_count();
-        if ((double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
-        if (wide) {
+        {
             const int box = WIDE_W * chans;
-            if ((rc = fill_desc(fp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-            if ((rc = fill_desc(fp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-            if ((rc = fill_desc(fp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-            if ((rc = fill_desc(fp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-            if ((rc = fill_desc(fp.y, y, out_dtype, B, L, D, out_stride_b, out_stride_l, box, TB, tma))) return rc;
-            if ((rc = fill_desc(fp.hs, h_saved, QSSM_F32, B, L, D, hs_sb, hs_sl, box, TB, tma))) return rc;
             const long long ctas = (groups + rounds - 1) / rounds;  // equal rounds, at most one CTA per SM
             const int stage4 = nin * TB * box * es;
             const int outbuf4 = TB * box * eo + (save_h ? TB * box * 4 : 0);
-            const int n_out4 = env_int("QSSM_NOUT", 2) == 3 ? 3 : 2;
+            const int n_out4 = knob(K_NOUT, 2) == 3 ? 3 : 2;
             fp.g.n_out = n_out4;
             // measured (bf16, h stored): 3 stages 0.559 ms on the cfg1 shape and 4.72 ms on cfg4, 4 stages
             // 0.613 / 4.95 ms, 2 stages 0.669 / 4.98 ms; two or three staging tiles make no difference
@@ -701,7 +804,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
 
     const int stage = nin * TB * chans * es;
     const int outbuf = TB * chans * eo + (h_saved != nullptr ? TB * chans * 4 : 0);
-    int n_out = env_int("QSSM_NOUT", 3);
+    int n_out = knob(K_NOUT, 3);
     if (n_out < 2) n_out = 2;
     if (n_out > 4) n_out = 4;
     fp.g.n_out = n_out;
@@ -726,9 +829,17 @@ int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const v
                             int in_dtype, int out_dtype, int n_seg_req, int* status_word, void* stream) {
     int rc = check_common(B, L, D, in_dtype, out_dtype);
     if (rc) return rc;
-    // Scratch the segmented scan would need; refuse rather than quietly run unsegmented.
-    const int n_seg = n_seg_req != 0 ? (n_seg_req < 0 ? -n_seg_req : n_seg_req) : auto_segments(B, L, D, in_dtype);
-    const size_t need = ws_bytes_for(B, D, n_seg);
+    // "aggregates already in ws" has no meaning here: no aggregate entry point writes the built-in array
+    if (n_seg_req < 0) return QSSM_E_SHAPE;
+    // Scratch the call would use; refuse rather than quietly run another way.  With n_seg = 0 the library
+    // may pick the single-pass kernels for few-chain shapes, whose ticket and descriptor area then lives in
+    // the array too (and is zeroed by a memset on the stream at the start of the call).
+    const int n_seg = n_seg_req != 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
+    size_t need = ws_bytes_for(B, D, n_seg);
+    if (n_seg_req == 0 && h_saved == nullptr) {
+        const size_t chained = chained_ws_bytes(B, L, D, in_dtype);
+        if (chained > need) need = chained;
+    }
     if (need > (size_t)QSSM_STATIC_WS_BYTES) return QSSM_E_STATIC_WS;
     void* ws = nullptr;
     if ((rc = static_ws_address(&ws))) return rc;
@@ -762,7 +873,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     if ((rc = check_strides(L, D, dy_stride_b, dy_stride_l))) return rc;
 
     // Few chains, long sequence: single-pass chained kernel (h rebuilt from tile_h only).
-    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && env_int("QSSM_NO_TMA", 0) == 0) {
+    if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
         const size_t need = chained_ws_bytes(B, L, D, in_dtype);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         const long long n_tiles_b = (L + TS - 1) / TS;
@@ -781,10 +892,10 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
             g.n_dtiles = (int)((D + 63) / 64);
             g.n_seg = 1;
             g.use_tma = 1;
-            g.l2_hint = env_int("QSSM_CHAINED_HINT", 1);
+            g.l2_hint = knob(K_CHAINED_HINT, 1);
             g.status = status_word;
             g.n_chains = lay.n_chains;
-            g.n_stages = env_int("QSSM_STAGES", 0) >= 2 && env_int("QSSM_STAGES", 0) <= 8 ? env_int("QSSM_STAGES", 0)
+            g.n_stages = knob(K_STAGES, 0) >= 2 && knob(K_STAGES, 0) <= 8 ? knob(K_STAGES, 0)
                                                                                           : (es == 2 ? 2 : 4);
             const int chans = 64;
             BwdParams& f = cp.f;
@@ -853,50 +964,38 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     const bool saved = h_saved != nullptr;
     const long long n_tiles_b = (L + TS - 1) / TS;
     const long long g_sb = L * D, g_sl = D;  // gradients and h_saved are contiguous
-    bool tma = env_int("QSSM_NO_TMA", 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
+    bool tma = knob(K_NO_TMA, 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
                tma_ok(c, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(dy, B, L, D, dy_stride_b, dy_stride_l, eo) &&
                tma_ok(dx, B, L, D, g_sb, g_sl, es) && tma_ok(da, B, L, D, g_sb, g_sl, es) &&
                tma_ok(db, B, L, D, g_sb, g_sl, es) && tma_ok(dc, B, L, D, g_sb, g_sl, es) &&
                (saved ? tma_ok(h_saved, B, L, D, g_sb, g_sl, 4) : tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4));
     bp.g.use_tma = tma ? 1 : 0;
-    if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, chans, TB, tma))) return rc;
-    if (saved)
-        rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, chans, TB + 1, tma);
-    else
-        rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, chans, TB / TS, tma);
-    if (rc) return rc;
     // Four adjacent strips per CTA, loaded and stored as one 512-byte-wide tile per tensor (16-bit storage).
     // One such CTA fits per SM, so the groups must fill whole rounds of SM-count CTAs reasonably well;
     // otherwise (e.g. 152 groups on 148 SMs) the one-warp-per-CTA kernel, which packs finer, is used.
-    bool wide = tma && env_int("QSSM_WIDE", 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W;
+    bool wide = tma && knob(K_WIDE, 1) != 0 && es == 2 && pl.V == 2 && TB == TS && pl.g.n_dtiles >= WIDE_W;
     if (wide) {
         const long long groups = B * n_seg * ((pl.g.n_dtiles + WIDE_W - 1) / WIDE_W);
         const long long rounds = (groups + sm_count() - 1) / sm_count();
         if ((double)groups / (double)(rounds * sm_count()) < 0.85) wide = false;
     }
-    const int out_box = wide ? WIDE_W * chans : chans;
-    if (wide) {  // re-encode the inputs with four-strip boxes
-        const int box = WIDE_W * chans;
-        if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-        if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-        if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-        if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
-        if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, box, TB, tma))) return rc;
-        if (saved)
-            rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, box, TB + 1, tma);
-        else
-            rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, box, 1, tma);
-        if (rc) return rc;
-    }
-    if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
-    if ((rc = fill_desc(bp.dc, dc, in_dtype, B, L, D, g_sb, g_sl, out_box, TB, tma))) return rc;
+    // tensor maps, encoded once with the box of the kernel that will run
+    const int box = wide ? WIDE_W * chans : chans;
+    if ((rc = fill_desc(bp.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.b, b, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.c, c, in_dtype, B, L, D, in_stride_b, in_stride_l, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.dy, dy, out_dtype, B, L, D, dy_stride_b, dy_stride_l, box, TB, tma))) return rc;
+    if (saved)
+        rc = fill_desc(bp.hsrc, h_saved, QSSM_F32, B, L, D, g_sb, g_sl, box, TB + 1, tma);
+    else
+        rc = fill_desc(bp.hsrc, tile_h, QSSM_F32, B, n_tiles_b, D, n_tiles_b * D, D, box, wide ? 1 : TB / TS, tma);
+    if (rc) return rc;
+    if ((rc = fill_desc(bp.dx, dx, in_dtype, B, L, D, g_sb, g_sl, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.da, da, in_dtype, B, L, D, g_sb, g_sl, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.db, db, in_dtype, B, L, D, g_sb, g_sl, box, TB, tma))) return rc;
+    if ((rc = fill_desc(bp.dc, dc, in_dtype, B, L, D, g_sb, g_sl, box, TB, tma))) return rc;
     bp.h_in = h_in;
     bp.g_in = seeds;
     bp.g_first = g_first;

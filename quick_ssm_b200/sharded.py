@@ -34,33 +34,34 @@ class CudaShardOps:
     def __init__(self):
         self._ws_fwd = None  # (workspace, segments) left by aggregate_fwd for the next forward
         self._ws_bwd = None
+        self._ws_cache = {}
 
-    @staticmethod
-    def _segments(t):
+    def _segments(self, t, which):
         B, L, D = t.shape
         k = _lib.auto_segments(B, L, D, t.dtype)
-        ws = torch.empty(3 * B * k * D * 4, dtype=torch.uint8, device=t.device) if k > 1 else None
+        if k <= 1:
+            return k, None
+        key = (which, t.device, B, k, D)
+        ws = self._ws_cache.get(key)
+        if ws is None:
+            ws = torch.empty(3 * B * k * D * 4, dtype=torch.uint8, device=t.device)
+            self._ws_cache[key] = ws
         return k, ws
 
-    def aggregate_fwd(self, x, a, b):
-        B, L, D = x.shape
-        A = torch.empty((B, D), dtype=torch.float32, device=x.device)
-        H = torch.empty_like(A)
-        k, ws = self._segments(x)
+    def aggregate_fwd(self, x, a, b, A, H):
+        """(A, H) [B, D] fp32 views receive (prod a, end state from a zero start)."""
+        k, ws = self._segments(x, "f")
         _lib.aggregate_fwd(x, a, b, A, H, n_seg=k, ws=ws)
         self._ws_fwd = (ws, k) if k > 1 else None
-        return A, H
 
-    def aggregate_bwd(self, a, c, dy):
-        B, L, D = a.shape
-        P = torch.empty((B, D), dtype=torch.float32, device=a.device)
-        Q = torch.empty_like(P)
-        k, ws = self._segments(a)
+    def aggregate_bwd(self, a, c, dy, P, Q):
+        """(P, Q) [B, D] fp32 views receive (prod a, a(t0)*dh(t0) from a zero carry)."""
+        k, ws = self._segments(a, "b")
         _lib.aggregate_bwd(a, c, dy, P, Q, n_seg=k, ws=ws)
         self._ws_bwd = (ws, k) if k > 1 else None
-        return P, Q
 
     def fold(self, A, H, upto: int, reverse: bool):
+        """A, H: [G, B, D] views (any stride between ranks) of the gathered aggregates."""
         return _lib.carry_fold(A, H, upto, reverse=reverse)
 
     def forward(self, x, a, b, c, y, tile_h, h_in):
@@ -80,47 +81,128 @@ class CudaShardOps:
             _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h, g_in=g_in)
 
 
-def _gather(pair, group):
-    """All-gather a (first, second) pair of [B, D] fp32 tensors -> two [G, B, D] stacks."""
-    packed = torch.stack(pair).contiguous()
-    world = dist.get_world_size(group)
-    parts = [torch.empty_like(packed) for _ in range(world)]
-    dist.all_gather(parts, packed, group=group)
-    full = torch.stack(parts)  # [G, 2, B, D]
-    return full[:, 0].contiguous(), full[:, 1].contiguous()
+class TorchComm:
+    """The one collective a sequence shard needs, over a ``torch.distributed`` process group."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+    def all_gather(self, full: torch.Tensor, send: torch.Tensor) -> None:
+        """``full[r] = send of rank r`` for every rank r; ordered on the calling stream."""
+        dist.all_gather_into_tensor(full.view(-1, *send.shape[1:]), send, group=self.group)
 
 
-def shard_forward(ops, group, xs, as_, bs, cs, k_out, keep_boundaries: bool):
-    """Forward of one sequence shard (no autograd): returns ``(y, tile_h or None)``."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+def _as_comm(group):
+    return group if hasattr(group, "all_gather") else TorchComm(group)
+
+
+class Exchange:
+    """The carry exchange of one direction: a ``[2, B, D]`` send buffer the aggregate kernel writes
+    into, one all-gather into a ``[G, 2, B, D]`` buffer, and views of that buffer for the fold - no
+    packing, stacking or copies around the collective.  Buffers are kept per (direction, device,
+    B, D, communicator) and reused from call to call: every user is ordered on the calling stream
+    (the collective makes that stream wait for it)."""
+
+    _cache = {}
+
+    def __init__(self, comm, which: str, B: int, D: int, device):
+        self.comm = comm
+        key = (which, str(device), B, D, comm.world, id(getattr(comm, "group", comm)))
+        bufs = Exchange._cache.get(key)
+        if bufs is None:
+            send = torch.empty((2, B, D), dtype=torch.float32, device=device)
+            full = torch.empty((comm.world, 2, B, D), dtype=torch.float32, device=device)
+            bufs = Exchange._cache[key] = (send, full)
+        self.send, self.full = bufs
+
+    def set_identity(self):
+        self.send[0].fill_(1.0)
+        self.send[1].zero_()
+
+    def gather(self):
+        """Returns the ``[G, B, D]`` views (first, second) of every rank's pair."""
+        self.comm.all_gather(self.full, self.send)
+        return self.full[:, 0], self.full[:, 1]
+
+
+def forward_aggregate(ops, comm, xs, as_, bs) -> Exchange:
+    """First half of a shard's forward: its aggregate, written into the send buffer of the exchange."""
     B, L, D = xs.shape
-    if rank == world - 1:  # nobody comes after the last shard: identity aggregate, no read
-        A = torch.ones((B, D), dtype=torch.float32, device=xs.device)
-        H = torch.zeros_like(A)
+    ex = Exchange(comm, "f", B, D, xs.device)
+    if comm.rank == comm.world - 1:  # nobody comes after the last shard: identity aggregate, no read
+        ex.set_identity()
     else:
-        A, H = ops.aggregate_fwd(xs, as_, bs)
-    A_all, H_all = _gather((A, H), group)
-    h_in = ops.fold(A_all, H_all, rank, False)
-    y = torch.empty((B, L, D), dtype=k_out, device=xs.device)
-    tile_h = torch.empty((B, _n_tiles(L), D), dtype=torch.float32, device=xs.device) if keep_boundaries else None
+        ops.aggregate_fwd(xs, as_, bs, ex.send[0], ex.send[1])
+    return ex
+
+
+def forward_finish(ops, comm, ex: Exchange, xs, as_, bs, cs, y, tile_h, mark=lambda: None):
+    """Second half: all-gather, fold the shards before this one into ``h_in``, seeded scan."""
+    A_all, H_all = ex.gather()
+    h_in = ops.fold(A_all, H_all, comm.rank, False)
+    mark()
     ops.forward(xs, as_, bs, cs, y, tile_h, h_in)
-    return y, tile_h
 
 
-def shard_backward(ops, group, xs, as_, bs, cs, dy, tile_h):
-    """Backward of one sequence shard (no autograd): returns ``[dx, da, db, dc]`` in the input dtype."""
-    rank = dist.get_rank(group)
-    B, L, D = xs.shape
-    if rank == 0:  # nobody comes before the first shard
-        P = torch.ones((B, D), dtype=torch.float32, device=xs.device)
-        Q = torch.zeros_like(P)
+def backward_aggregate(ops, comm, as_, cs, dy) -> Exchange:
+    B, L, D = as_.shape
+    ex = Exchange(comm, "b", B, D, as_.device)
+    if comm.rank == 0:  # nobody comes before the first shard
+        ex.set_identity()
     else:
-        P, Q = ops.aggregate_bwd(as_, cs, dy)
-    P_all, Q_all = _gather((P, Q), group)
-    g_in = ops.fold(P_all, Q_all, rank, True)
-    grads = [torch.empty(xs.shape, dtype=xs.dtype, device=xs.device) for _ in range(4)]
+        ops.aggregate_bwd(as_, cs, dy, ex.send[0], ex.send[1])
+    return ex
+
+
+def backward_finish(ops, comm, ex: Exchange, xs, as_, bs, cs, dy, tile_h, grads, mark=lambda: None):
+    P_all, Q_all = ex.gather()
+    g_in = ops.fold(P_all, Q_all, comm.rank, True)
+    mark()
     ops.backward(xs, as_, bs, cs, dy, tile_h, g_in, grads)
+
+
+def shard_forward(ops, group, xs, as_, bs, cs, k_out, keep_boundaries: bool, *, y=None, tile_h=None, marks=None):
+    """Forward of one sequence shard (no autograd): returns ``(y, tile_h or None)``.
+
+    ``group``: a process group (or None for the default one), or any object with ``rank``,
+    ``world`` and ``all_gather(full, send)``.  ``y`` / ``tile_h`` may be passed in preallocated.
+    ``marks``, if a list, receives four CUDA events on the calling stream: start, aggregate done,
+    exchange and fold done, scan done."""
+    comm = _as_comm(group)
+    B, L, D = xs.shape
+    mark = (lambda: marks.append(_event(xs.device))) if marks is not None else (lambda: None)
+    mark()
+    ex = forward_aggregate(ops, comm, xs, as_, bs)
+    mark()
+    if y is None:
+        y = torch.empty((B, L, D), dtype=k_out, device=xs.device)
+    if keep_boundaries and tile_h is None:
+        tile_h = torch.empty((B, _n_tiles(L), D), dtype=torch.float32, device=xs.device)
+    forward_finish(ops, comm, ex, xs, as_, bs, cs, y, tile_h if keep_boundaries else None, mark)
+    mark()
+    return y, (tile_h if keep_boundaries else None)
+
+
+def shard_backward(ops, group, xs, as_, bs, cs, dy, tile_h, *, grads=None, marks=None):
+    """Backward of one sequence shard (no autograd): returns ``[dx, da, db, dc]`` in the input dtype."""
+    comm = _as_comm(group)
+    mark = (lambda: marks.append(_event(xs.device))) if marks is not None else (lambda: None)
+    mark()
+    ex = backward_aggregate(ops, comm, as_, cs, dy)
+    mark()
+    if grads is None:
+        grads = [torch.empty(xs.shape, dtype=xs.dtype, device=xs.device) for _ in range(4)]
+    backward_finish(ops, comm, ex, xs, as_, bs, cs, dy, tile_h, grads, mark)
+    mark()
     return grads
+
+
+def _event(device):
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record(torch.cuda.current_stream(device))
+    return ev
 
 
 class _SequenceShardedScan(torch.autograd.Function):

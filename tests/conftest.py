@@ -24,3 +24,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def tune():
+    """Set launch-shape knobs of the library for one test: ``tune("CHUNK_ROWS", 64)``.  Every knob
+    goes back to its start-up value afterwards."""
+    from quick_ssm_b200 import _lib
+
+    def _set(name, value):
+        _lib.tune_set(name, int(value))
+
+    yield _set
+    _lib.tune_reset()

@@ -58,6 +58,20 @@ def test_argument_validation_without_gpu():
     assert lib.qssm_scan_fwd_static_ws(one, one, one, one, one, None, None, None, None,
                                        4, 16384, 2048, 16384 * 2048, 2048, 16384 * 2048, 2048,
                                        2, 2, 64, None, None) == -8
+    # built-in scratch: "aggregates already in ws" cannot be true of the library's own array
+    assert lib.qssm_scan_fwd_static_ws(one, one, one, one, one, None, None, None, None,
+                                       1, 4096, 64, 4096 * 64, 64, 4096 * 64, 64, 0, 0, -4, None, None) == -2
+
+
+def test_tuning_knobs_by_name():
+    lib = _lib.load()
+    assert lib.qssm_tune_set(b"CHUNK_ROWS", 64) == 0
+    assert lib.qssm_tune_set(b"QSSM_CHUNK_ROWS", 128) == 0   # the environment spelling is accepted too
+    assert lib.qssm_tune_set(b"NO_SUCH_KNOB", 1) == -2
+    assert lib.qssm_tune_set(None, 1) == -1
+    lib.qssm_tune_reset()
+    with pytest.raises(KeyError):
+        _lib.tune_set("nope", 1)
 
 
 def test_workspace_and_segment_policy():

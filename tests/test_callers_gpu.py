@@ -105,26 +105,38 @@ def test_sequence_sharded_scan_over_nccl(tmp_path, dtype):
         check(got[k], ref, k)
 
 
-def test_streaming_chunks_equal_one_scan():
-    """Pieces of a sequence fed one after the other with the carried state reproduce the whole scan;
-    includes single-step pieces (token-by-token decoding) and an empty piece."""
-    from quick_ssm_b200 import scan
+def test_streaming_pieces_match_the_seeded_oracle():
+    """Pieces of a sequence fed one after the other with the carried state: every piece is checked
+    against the CPU oracle run on that piece with the oracle's own carried state (``h_in``), and the
+    concatenation against the oracle over the whole sequence.  Includes single-step pieces
+    (token-by-token decoding) and an empty piece."""
     from quick_ssm_b200.streaming import ScanState, scan_chunk
+    from tolerances import assert_close_f32, assert_close_half
     for dtype in (torch.float32, torch.bfloat16):
-        inp = make_inputs(3, 301, 72, dtype=dtype, seed=17).to("cuda")
-        whole = scan(*inp.tensors())
+        inp = make_inputs(3, 301, 72, dtype=dtype, seed=17)
+        dev = inp.to("cuda")
+        acc = np.float64 if dtype == torch.float32 else np.float32
+        check = assert_close_f32 if dtype == torch.float32 else assert_close_half
+        f = [t.float() for t in inp.tensors()]
+        _, y_whole, h_whole = so.scan_forward(*f, dtype=acc)
         state, outs, pos = None, [], 0
+        ref_state = np.zeros((3, 72), dtype=acc)
         for piece in (1, 1, 30, 0, 16, 17, 200, 36):
             sl = slice(pos, pos + piece)
-            y, state = scan_chunk(inp.x[:, sl], inp.a[:, sl], inp.b[:, sl], inp.c[:, sl], state)
+            y, state = scan_chunk(dev.x[:, sl], dev.a[:, sl], dev.b[:, sl], dev.c[:, sl], state)
+            if piece > 0:
+                _, y_ref, ref_state = so.scan_forward(*(t[:, sl] for t in f), dtype=acc, h_in=ref_state)
+                check(y, y_ref, f"y of piece [{pos}, {pos + piece})")
+            check(state.h, ref_state, f"state after step {pos + piece}")
             outs.append(y)
             pos += piece
         assert pos == 301
-        got = torch.cat(outs, dim=1)
-        tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-3)
-        assert torch.allclose(got.float(), whole.float(), **tol)
-        h_all, _ = scan_chunk(inp.x, inp.a, inp.b, None, ScanState.zeros(3, 72))
-        assert torch.allclose(state.h, h_all[:, -1].float(), rtol=2e-2 if dtype != torch.float32 else 1e-5, atol=1e-3)
+        check(torch.cat(outs, dim=1), y_whole, "concatenated pieces")
+        check(state.h, h_whole, "final state")
+        # h itself (no output gate), seeded with an explicit zero state
+        h_all, last = scan_chunk(dev.x, dev.a, dev.b, None, ScanState.zeros(3, 72))
+        check(h_all, so.scan_forward(*f[:3], dtype=acc)[0], "h")
+        check(last.h, h_whole, "h_last")
     _lib.check_device_status(synchronize=True)
 
 

@@ -293,12 +293,12 @@ def test_segment_aggregates_are_reused_by_the_scan():
 @pytest.mark.parametrize("dtype,shape", [(torch.float32, (1, 5000, 72)), (torch.bfloat16, (2, 3001, 200)),
                                          (torch.float16, (3, 700, 64))], ids=["fp32", "bf16", "fp16"])
 @pytest.mark.parametrize("chunk_rows", [64, 256])
-def test_chained_single_pass_forward(monkeypatch, dtype, shape, chunk_rows):
+def test_chained_single_pass_forward(tune, dtype, shape, chunk_rows):
     """The single-pass forward for few chains (chunks claimed from a ticket counter, carries found by
     looking back over chunk descriptors), forced on small shapes: forward, boundary states (through the
     backward that consumes them), seed and end state."""
-    monkeypatch.setenv("QSSM_CHAINED", "2")
-    monkeypatch.setenv("QSSM_CHUNK_ROWS", str(chunk_rows))
+    tune("CHAINED", "2")
+    tune("CHUNK_ROWS", str(chunk_rows))
     inp = make_inputs(*shape, dtype=dtype, seed=23)
     ref = _oracle(inp, np.float64 if dtype == torch.float32 else np.float32)
     got = _run_scan(inp)
@@ -310,7 +310,7 @@ def test_chained_single_pass_forward(monkeypatch, dtype, shape, chunk_rows):
     y = torch.empty_like(x)
     h_last = torch.empty(B, D, device=DEV)
     _lib.scan_fwd(x, a, b, c, y, h_in=h0, h_last=h_last)
-    monkeypatch.setenv("QSSM_CHAINED", "0")
+    tune("CHAINED", "0")
     y_ref = torch.empty_like(x)
     h_ref = torch.empty(B, D, device=DEV)
     _lib.scan_fwd(x, a, b, c, y_ref, h_in=h0, h_last=h_ref, n_seg=1)
@@ -320,16 +320,16 @@ def test_chained_single_pass_forward(monkeypatch, dtype, shape, chunk_rows):
     assert torch.allclose(h_last, h_ref, rtol=1e-4, atol=1e-5)
 
 
-def test_chained_single_pass_is_deterministic(monkeypatch):
+def test_chained_single_pass_is_deterministic(tune):
     """Chunks run concurrently and find their carries in whatever state the predecessors are in, but the
     carry is always folded chunk by chunk in time order: results are bit-identical from run to run and
     for any number of warps working at once."""
-    monkeypatch.setenv("QSSM_CHAINED", "2")
-    monkeypatch.setenv("QSSM_CHUNK_ROWS", "64")
+    tune("CHAINED", "2")
+    tune("CHUNK_ROWS", "64")
     inp = make_inputs(2, 20000, 128, dtype=torch.bfloat16, seed=31)
     runs = []
     for grid in ("0", "0", "37", "1000"):
-        monkeypatch.setenv("QSSM_CHAINED_GRID", grid)
+        tune("CHAINED_GRID", grid)
         runs.append(_run_scan(inp))
     for other in runs[1:]:
         for k in runs[0]:
@@ -369,14 +369,14 @@ def test_no_write_outside_the_outputs(shape, dtype):
 @pytest.mark.parametrize("env", [{"QSSM_V": "1"}, {"QSSM_V": "2"}, {"QSSM_TB": "32"}, {"QSSM_V": "1", "QSSM_TB": "32"},
                                  {"QSSM_WIDE": "0"}, {"QSSM_NO_TMA": "1"}, {"QSSM_STAGES": "2"}],
                          ids=lambda e: "_".join(f"{k[5:]}{v}" for k, v in e.items()))
-def test_every_kernel_variant_gives_the_same_answer(monkeypatch, env):
+def test_every_kernel_variant_gives_the_same_answer(tune, env):
     """Strip width, tile height, ring depth, wide/narrow stores and the guarded path are launch-shape
     choices: forcing each of them must not change the result beyond fp32 rounding."""
     inp = make_inputs(2, 700, 330, dtype=torch.bfloat16, seed=43)
     ref = _oracle(inp, np.float32)
     base = _run_scan(inp)
     for k, v in env.items():
-        monkeypatch.setenv(k, v)
+        tune(k[5:], v)
     for checkpoint in (True, False):
         got = _run_scan(inp, checkpoint=checkpoint)
         _check(got, ref, torch.bfloat16)
@@ -390,39 +390,39 @@ def test_every_kernel_variant_gives_the_same_answer(monkeypatch, env):
                          ids=["bf16_full_strips", "fp16_ragged_channels", "bf16_fp32_out_ragged"])
 @pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
 @pytest.mark.parametrize("fwd_tile4", ["0", "1"], ids=["fwd_auto", "fwd_four_strips"])
-def test_four_strip_kernels_match_the_oracle(monkeypatch, shape, dtype, out_dtype, checkpoint, fwd_tile4):
+def test_four_strip_kernels_match_the_oracle(tune, shape, dtype, out_dtype, checkpoint, fwd_tile4):
     """Shapes wide enough for the kernels that give a CTA four adjacent strips (16-bit storage, enough
     groups of four strips to fill the GPU): a partial last tile in time, a channel count that leaves the
     last group with fewer than four strips and a partial strip, fp32 y/dy, stored h and recompute.  The
     forward takes the four-strip kernel by itself only when it stores h; QSSM_FWD_TILE4=1 forces it for
     the other forwards too.  Narrow kernels on the same input must agree within rounding."""
-    monkeypatch.setenv("QSSM_FWD_TILE4", fwd_tile4)
+    tune("FWD_TILE4", fwd_tile4)
     inp = make_inputs(*shape, dtype=dtype, out_dtype=out_dtype, seed=47)
     ref = _oracle(inp, np.float32)
     got = _run_scan(inp, checkpoint=checkpoint, out_dtype=out_dtype)
     _check(got, ref, dtype)
-    monkeypatch.setenv("QSSM_WIDE", "0")
+    tune("WIDE", "0")
     narrow = _run_scan(inp, checkpoint=checkpoint, out_dtype=out_dtype)
     for k in got:
         assert torch.allclose(got[k].float(), narrow[k].float(), rtol=2e-2, atol=1e-3), k
 
 
-def test_expired_wait_is_reported_and_the_context_survives(monkeypatch):
+def test_expired_wait_is_reported_and_the_context_survives(tune):
     """The failure path of the bounded waits, on a healthy GPU: a test hook starts the chunk counter of
     the single-pass kernel past the first chunk of every chain, so nothing ever publishes those chunks;
     the look-back waits of the other chunks run into their (shortened) limit, the kernel records the
     status code and returns, the host raises, and the next launch works as usual."""
-    monkeypatch.setenv("QSSM_CHAINED", "2")
-    monkeypatch.setenv("QSSM_CHUNK_ROWS", "64")
-    monkeypatch.setenv("QSSM_WAIT_MS", "100")
+    tune("CHAINED", "2")
+    tune("CHUNK_ROWS", "64")
+    tune("WAIT_MS", "100")
     inp = make_inputs(1, 2000, 64, dtype=torch.float32, seed=51).to(DEV)
     x, a, b, c = inp.tensors()
     y = torch.empty_like(x)
-    monkeypatch.setenv("QSSM_TEST_SKIP_FIRST_CHUNK", "1")
+    tune("TEST_SKIP_FIRST_CHUNK", "1")
     _lib.scan_fwd(x, a, b, c, y)  # launches fine; the error is found on the device
     with pytest.raises(RuntimeError, match="expired"):
         _lib.check_device_status(synchronize=True)
-    monkeypatch.delenv("QSSM_TEST_SKIP_FIRST_CHUNK")
+    tune("TEST_SKIP_FIRST_CHUNK", 0)
     _lib.scan_fwd(x, a, b, c, y)
     _lib.check_device_status(synchronize=True)
     ref = _oracle(inp, np.float64)

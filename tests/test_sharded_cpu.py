@@ -18,17 +18,18 @@ from quick_ssm_b200.synth import make_inputs
 class OracleShardOps:
     """CPU stand-in for CudaShardOps, float32 tensors only."""
 
-    def aggregate_fwd(self, x, a, b):
+    def aggregate_fwd(self, x, a, b, A_out, H_out):
         ones = np.ones((x.shape[0], x.shape[2]), dtype=np.float64)
         _, _, H = so.scan_forward(x, a, b)
         _, _, A = so.scan_forward(torch.zeros_like(x), a, torch.zeros_like(x), h_in=ones)
-        return torch.from_numpy(A).float(), torch.from_numpy(H).float()
+        A_out.copy_(torch.from_numpy(A))
+        H_out.copy_(torch.from_numpy(H))
 
-    def aggregate_bwd(self, a, c, dy):
+    def aggregate_bwd(self, a, c, dy, P_out, Q_out):
         z = torch.zeros_like(a)
         Q = so.scan_backward(z, a, z, c, dy)[4]
-        P = a.double().prod(dim=1).float()
-        return P, torch.from_numpy(Q).float()
+        P_out.copy_(a.double().prod(dim=1))
+        Q_out.copy_(torch.from_numpy(Q))
 
     def fold(self, A, H, upto, reverse):
         run = torch.zeros_like(A[0])
