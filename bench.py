@@ -12,6 +12,17 @@ batch/channel shard of an N-times larger problem: the recurrences are independen
 no collective on the data path (weak scaling).  Time is taken on the device with CUDA events,
 max over ranks.
 
+The same line carries, outside the headline value:
+  forward_only   the two inference forms on the same workload: y under no_grad (5 tensor passes)
+                 and h only (forward_only, 4 passes);
+  api            the same step through the Python API, scan(...) + .backward() (autograd, allocations);
+  host_call_us   host time of one qssm_scan_fwd + qssm_scan_bwd call pair on a tiny shape;
+  seq_sharded    the long-sequence configuration (B=1, L=2^20, D=2048, fp16, decay close to one) with
+                 the TIME axis split over the N ranks: per rank one aggregate pass, one NCCL all-gather
+                 of 2*B*D floats, a fold and a seeded scan, forward and backward; at N=1 the single-pass
+                 kernels.  One 64-channel strip of the result is checked against the CPU oracle outside
+                 the timed region.
+
 --impl reference times the CPU implementation of the same path (the sequential-loop oracle,
 all host threads) on a bounded sample of the same workload and prints the same JSON line.
 """
@@ -34,10 +45,22 @@ UNIT = "Gelem/s"
 CFG = dict(B=8, L=8192, D=4096)
 WORKLOAD = "cfg1: scan fwd+bwd, B=8 L=8192 D=4096, bf16 storage / fp32 accumulate, checkpoint=True"
 
-# DRAM bytes (read + write) of one backward launch, from an ncu capture of the same kernel on a
-# quarter of the sequence (`--seq-len 2048`: same chains, same residency, 1.3 GB resident);
-# traffic grows in proportion to L, so a full launch is this times L/2048.
-NCU_BWD_TRAFFIC_BYTES_L2048 = 687.91e6 + 492.08e6
+CFG2 = dict(B=1, L=1 << 20, D=2048)
+HOST_CPUS = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+# DRAM bytes (read + write) of one backward launch come from an ncu capture of the same kernel on a
+# shorter sequence (same chains, same residency); the capture's figures and the commit it was taken
+# at live in this file, which the ncu summary beside it quotes too.  Traffic grows in proportion to L.
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "scan_bwd_tile4_cfg1_traffic.json")
+
+
+def _ncu_traffic(L: int):
+    try:
+        with open(TRAFFIC_FILE) as f:
+            t = json.load(f)
+        return (float(t["dram_bytes_read"]) + float(t["dram_bytes_write"])) * (L / float(t["L"])), t.get("commit")
+    except Exception:
+        return None, None
 
 
 def _peak_hbm():
@@ -123,6 +146,7 @@ def _cpu_sample_inputs(sample_b: int):
 def cpu_baseline(budget_s: float = 12.0, sample_b: int = 1):
     """Sequential-loop oracle (C, OpenMP over channels) on a batch slice of the workload."""
     from oracle import scan_oracle as so
+    so.set_num_threads(HOST_CPUS)  # every host core, whatever OMP_NUM_THREADS the launcher set
     arrs, outs = _cpu_sample_inputs(sample_b)
     x, a, b, c, dy = arrs
     n = x.size
@@ -145,6 +169,7 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import scan_oracle as so
+    so.set_num_threads(HOST_CPUS)  # torch.distributed.run exports OMP_NUM_THREADS=1: do not inherit it
     sample_b = 1
     arrs, outs = _cpu_sample_inputs(sample_b)
     x, a, b, c, dy = arrs
@@ -172,8 +197,232 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm: pieces measured next to the headline step
 # ---------------------------------------------------------------------------------------------
+def _timed_ms(torch, fn, steps, sync, warmup=3):
+    """Mean device time of `steps` back-to-back calls (CUDA events on the launching stream)."""
+    for _ in range(warmup):
+        fn()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / steps
+
+
+def measure_forward_only(torch, _lib, x, a, b, c, y, steps, sync, peak):
+    """Inference forms of the forward on the headline workload (reference: scan() under no_grad,
+    scan_interface.py:169-213, and forward_only.block_scan_forward_3d, forward_only.py:423-540)."""
+    n, es = x.numel(), x.element_size()
+    out = {}
+    for name, cc, passes in (("y_no_grad", c, 5), ("h_only", None, 4)):
+        ms = _timed_ms(torch, lambda: _lib.scan_fwd(x, a, b, cc, y), steps, sync)
+        gbs = n * passes * es / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "algorithmic_bytes": n * passes * es, "achieved": gbs, "unit": "GB/s",
+                     "frac": gbs / peak, "gelems": n / (ms * 1e-3) / 1e9}
+    return out
+
+
+def measure_api(torch, x, a, b, c, dy, steps, sync):
+    """The same step through the public Python API: scan(...) then .backward() (autograd graph, output
+    and gradient allocations from the caching allocator on every step)."""
+    from quick_ssm_b200 import scan
+    leaves = [t.detach().requires_grad_() for t in (x, a, b, c)]
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        scan(*leaves, block_l=256, checkpoint=True).backward(dy)
+
+    ms = _timed_ms(torch, step, steps, sync)
+    for t in leaves:
+        t.grad = None
+    return {"ms_per_step": ms, "gelems": x.numel() / (ms * 1e-3) / 1e9, "steps": steps,
+            "path": "quick_ssm_b200.scan(x, a, b, c, block_l=256, checkpoint=True) + y.backward(dy)"}
+
+
+def measure_host_call(torch, _lib, dev, calls=1000):
+    """Host time of one forward + backward call pair through the binding on the copy-task shape of the
+    reference's training demo (copy_train.py:35-38: B=32, L=16, state 1024), and its device time."""
+    B, L, D = 32, 16, 1024
+    t = [torch.randn(B, L, D, device=dev, dtype=torch.bfloat16) for _ in range(5)]
+    y = torch.empty_like(t[0])
+    th = torch.empty((B, 1, D), dtype=torch.float32, device=dev)
+    g = [torch.empty_like(t[0]) for _ in range(4)]
+
+    def pair():
+        _lib.scan_fwd(t[0], t[1], t[2], t[3], y, tile_h=th)
+        _lib.scan_bwd(t[0], t[1], t[2], t[3], t[4], *g, tile_h=th)
+
+    for _ in range(20):
+        pair()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(calls):
+        pair()
+    host_us = (time.perf_counter() - t0) / calls * 1e6
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return {"host_us_per_fwd_bwd_pair": host_us, "device_us_per_pair": e0.elapsed_time(e1) / calls * 1e3,
+            "shape": [B, L, D], "calls": calls}
+
+
+def _strip_check(np, strips, ref_fn):
+    """|got - ref| <= 1e-3 * max(1, max|ref|) + 2e-2 * |ref| per tensor (16-bit storage against the
+    fp32 sequential loop; gradients of a 2^20-step chain with decay close to one reach hundreds, so the
+    absolute floor scales with the tensor's magnitude)."""
+    refs = ref_fn()
+    report, ok = {}, True
+    for name in ("y", "dx", "da", "db", "dc"):
+        g, r = strips[name].astype(np.float64), refs[name].astype(np.float64)
+        scale = max(1.0, float(np.abs(r).max()))
+        bad = np.abs(g - r) > 1e-3 * scale + 2e-2 * np.abs(r)
+        report[name] = {"max_abs_err": float(np.abs(g - r).max()), "max_abs_ref": float(np.abs(r).max()),
+                        "outside": int(bad.sum())}
+        ok = ok and not bad.any() and bool(np.isfinite(g).all())
+    return ok, report
+
+
+def measure_seq_sharded(torch, dist, _lib, dev, rank, world, steps, sync, peak):
+    """The long-sequence configuration with the time axis split over the ranks (see the module
+    docstring).  Returns the dict for the JSON line on rank 0, None elsewhere."""
+    import numpy as np
+    from quick_ssm_b200 import sharded
+    from quick_ssm_b200.synth import make_inputs
+
+    B, L, D = CFG2["B"], CFG2["L"], CFG2["D"]
+    Ls = L // world
+    dtype, es = torch.float16, 2
+    inp = make_inputs(B, Ls, D, dtype=dtype, device=dev, seed=0, rank=rank, decay="near_unit")
+    x, a, b, c = inp.tensors()
+    dy = inp.dy
+    y = torch.empty_like(x)
+    tile_h = torch.empty((B, (Ls + _lib.tile_rows() - 1) // _lib.tile_rows(), D), dtype=torch.float32, device=dev)
+    grads = [torch.empty_like(x) for _ in range(4)]
+
+    if world == 1:
+        def fwd(marks=None):
+            _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h)
+
+        def bwd(marks=None):
+            _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h)
+    else:
+        ops = sharded.CudaShardOps()
+        comm = sharded.TorchComm(None)
+
+        def fwd(marks=None):
+            sharded.shard_forward(ops, comm, x, a, b, c, dtype, True, y=y, tile_h=tile_h, marks=marks)
+
+        def bwd(marks=None):
+            sharded.shard_backward(ops, comm, x, a, b, c, dy, tile_h, grads=grads, marks=marks)
+
+    for _ in range(3):
+        fwd()
+        bwd()
+    sync()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+    marks_f, marks_b = [], []
+    ev[0].record()
+    for k in range(steps):
+        fwd(marks_f if world > 1 else None)
+        ev[2 * k + 1].record()
+        bwd(marks_b if world > 1 else None)
+        ev[2 * k + 2].record()
+    sync()
+    _lib.check_device_status(dev)
+    total_ms = ev[0].elapsed_time(ev[-1]) / steps
+    fwd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
+    bwd_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
+
+    def phases(marks):  # mean ms of (aggregate, all-gather + fold, seeded scan)
+        if not marks:
+            return [0.0, 0.0, 0.0]
+        k = len(marks) // 4
+        return [sum(marks[4 * i + j].elapsed_time(marks[4 * i + j + 1]) for i in range(k)) / k for j in range(3)]
+
+    mine = torch.tensor([total_ms, fwd_ms, bwd_ms] + phases(marks_f) + phases(marks_b), device=dev,
+                        dtype=torch.float64)
+    if world > 1:
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        table = torch.stack(allr).cpu()
+    else:
+        table = mine.cpu()[None]
+
+    # ---- one 64-channel strip, whole sequence, against the oracle (outside the timed region) ----
+    d0 = (D // 2 // 64) * 64
+    got = {"y": y, "dx": grads[0], "da": grads[1], "db": grads[2], "dc": grads[3]}
+    ins = {"x": x, "a": a, "b": b, "c": c, "dy": dy}
+    local = {k: v[:, :, d0:d0 + 64].contiguous() for k, v in {**got, **ins}.items()}
+    if world > 1:
+        whole = {}
+        for k, v in local.items():
+            parts = [torch.empty_like(v) for _ in range(world)] if rank == 0 else None
+            dist.gather(v, parts, dst=0)
+            if rank == 0:
+                whole[k] = torch.cat(parts, dim=1)
+    else:
+        whole = local
+    if rank != 0:
+        return None
+    from oracle import scan_oracle as so  # the checker, never the thing measured
+    host = {k: v.float().cpu().numpy() for k, v in whole.items()}
+
+    def ref_fn():
+        _, y_ref, _ = so.scan_forward(host["x"], host["a"], host["b"], host["c"], dtype=np.float32)
+        g = so.scan_backward(host["x"], host["a"], host["b"], host["c"], host["dy"], dtype=np.float32)
+        return {"y": y_ref, "dx": g[0], "da": g[1], "db": g[2], "dc": g[3]}
+
+    ok, report = _strip_check(np, host, ref_fn)
+    n_total = B * L * D
+    t_max = float(table[:, 0].max())
+    gelems = n_total / (t_max * 1e-3) / 1e9
+    gbs14 = n_total * 14 * es / (t_max * 1e-3) / 1e9
+    gbs20 = n_total * 20 * es / (t_max * 1e-3) / 1e9
+    out = {
+        "workload": "cfg2: B=1 L=2^20 D=2048 fp16, decay 1-10^U(-4,-1), fwd+bwd, checkpoint=True, "
+                    + ("single-pass kernels on one GPU" if world == 1 else f"time axis split over {world} ranks"),
+        "value": gelems, "unit": UNIT, "ms_per_step": t_max, "steps": steps, "scaling": "strong",
+        "fwd_ms_per_rank": [float(v) for v in table[:, 1]], "bwd_ms_per_rank": [float(v) for v in table[:, 2]],
+        "frac_of_14s_bytes": gbs14 / (world * peak),
+        "frac_of_20s_bytes": (gbs20 if world > 1 else gbs14) / (world * peak),
+        "bytes_note": "a shard reads the tensors its carry depends on twice (aggregate pass + scan): 20 tensor "
+                      "passes instead of 14 when the time axis is split; one GPU needs 14",
+        "parity": {"strip": [d0, d0 + 64], "rows": L, "ok": ok, "tensors": report,
+                   "rule": "|got-ref| <= 1e-3*max(1,max|ref|) + 2e-2*|ref| against the fp32 sequential loop"},
+    }
+    if world > 1:
+        names = ("aggregate_ms", "allgather_fold_ms", "scan_ms")
+        out["fwd_phases_per_rank"] = {n: [float(v) for v in table[:, 3 + j]] for j, n in enumerate(names)}
+        out["bwd_phases_per_rank"] = {n: [float(v) for v in table[:, 6 + j]] for j, n in enumerate(names)}
+        out["collective"] = "one NCCL all_gather_into_tensor of 2*B*D fp32 per rank and direction (16 KB per rank)"
+        out["gpu_launches_per_step"] = "fwd: aggregate + segment carry + fold + scan; bwd: the same"
+    return out
+
+
+def _bind_to_gpu_cpus(local: int):
+    """Run this rank on the CPUs NVML lists as local to its GPU, so that the pinned host buffers of
+    the end-to-end leg are first touched on that NUMA node.  A process setting; nothing on the GPU."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + j for i, w in enumerate(words) for j in range(64) if (int(w) >> j) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -188,6 +437,7 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device (no CPU path exists for the product)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    gpu_local_cpus = _bind_to_gpu_cpus(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -281,6 +531,24 @@ def run_gpu(args):
     barrier()
     copy_only_ms = e0.elapsed_time(e1) / e2e_steps
 
+    # ---- measured next to the headline: inference forwards, the Python API, host cost per call ----
+    extra_steps = max(5, min(K, 20))
+    peak, peak_kind = _peak_hbm()
+    fwd_only = api = host_call = None
+    if rank == 0:
+        fwd_only = measure_forward_only(torch, _lib, x, a, b, c, y, extra_steps, lambda: torch.cuda.synchronize(dev), peak)
+        api = measure_api(torch, x, a, b, c, dy, extra_steps, lambda: torch.cuda.synchronize(dev))
+        host_call = measure_host_call(torch, _lib, dev)
+    barrier()
+
+    # ---- the long-sequence configuration, time axis split over the ranks ----
+    h2d_bytes, d2h_bytes = pipe.h2d_bytes, pipe.d2h_bytes
+    del pipe, host, grads, y, tile_h, inp, x, a, b, c, dy
+    torch.cuda.empty_cache()
+    seq = None
+    if not args.no_seq:
+        seq = measure_seq_sharded(torch, dist, _lib, dev, rank, world, max(3, min(K, 10)), barrier, peak)
+
     if world > 1:
         t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms, copy_only_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -289,7 +557,7 @@ def run_gpu(args):
     if rank == 0:
         ms_per_step = total_ms / K
         value = world * n_elem / (ms_per_step * 1e-3) / 1e9
-        peak, peak_kind = _peak_hbm()
+        traffic, traffic_commit = _ncu_traffic(L)
         bwd_bytes = n_elem * 9 * es
         fwd_bytes = n_elem * 5 * es
         bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
@@ -304,7 +572,9 @@ def run_gpu(args):
                        "l2": "no flush needed: each step streams 7.5 GB of distinct tensors, far above the 126 MB L2"},
             "roofline": {"bound": "hbm", "kernel": "scan_bwd_tile4_kernel", "achieved": bwd_gbs, "peak": peak,
                          "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s",
-                         "frac": bwd_gbs / peak, "traffic": NCU_BWD_TRAFFIC_BYTES_L2048 * (L / 2048),
+                         "frac": bwd_gbs / peak, "traffic": traffic,
+                         "traffic_source": f"profiles/{os.path.basename(TRAFFIC_FILE)} (ncu capture at commit "
+                                           f"{traffic_commit}, scaled by L)",
                          "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
                          "ms_min_median_max": [bwd_all[0], bwd_all[K // 2], bwd_all[-1]],
                          "fwd": {"kernel": "scan_fwd_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
@@ -313,13 +583,15 @@ def run_gpu(args):
                          "step": {"achieved": step_gbs, "frac": step_gbs / peak,
                                   "roofline_gelems": peak / (14 * es)}},
             "e2e": {"value": world * n_elem / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
-                    "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "transfers_alone_ms_per_step": copy_only_ms,
+                    "cpus_local_to_gpu": gpu_local_cpus,
                     "path": "quick_ssm_b200.host.HostScan: pinned host buffers -> H2D -> qssm_scan_fwd/bwd -> D2H"},
             "gpu_launches": 2 * K * world,
             "gpu_launches_e2e": e2e_launches * world,
             "clocks": clocks.summary(),
+            "forward_only": fwd_only, "api": api, "host_call": host_call, "seq_sharded": seq,
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()
@@ -336,6 +608,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident loop only, no bench line")
+    ap.add_argument("--no-seq", action="store_true", help="skip the sequence-sharded long-sequence leg")
     ap.add_argument("--seq-len", type=int, default=0, help="profiling aid: shorter L (same chains, less memory)")
     args = ap.parse_args()
     if args.impl == "reference":

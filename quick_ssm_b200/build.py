@@ -41,6 +41,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-shared", "-Xcompiler", "-fPIC", "-o", LIB, SRC]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
+    extra = os.environ.get("QSSM_NVCC_FLAGS")  # e.g. -DQSSM_RESIDENT_SWEEP for measurement builds
+    if extra:
+        cmd[1:1] = extra.split()
     subprocess.check_call(cmd)
     return LIB
 

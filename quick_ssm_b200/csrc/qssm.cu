@@ -110,11 +110,11 @@ bool tma_ok(const void* ptr, long long B, long long L, long long D, long long sb
 // ---------------------------------------------------------------------------------------------
 enum Knob {
     K_GRID, K_V, K_TB, K_STAGES, K_NOUT, K_WIDE, K_FWD_TILE4, K_NO_TMA, K_L2HINT, K_CHAINED, K_CHUNK_ROWS,
-    K_CHAINED_GRID, K_CHAINED_HINT, K_WAIT_MS, K_DEBUG, K_RESIDENT, K_TEST_SKIP_FIRST_CHUNK, K_COUNT
+    K_CHAINED_GRID, K_CHAINED_HINT, K_WAIT_MS, K_DEBUG, K_TEST_SKIP_FIRST_CHUNK, K_COUNT
 };
 const char* const kKnobNames[K_COUNT] = {"GRID", "V", "TB", "STAGES", "NOUT", "WIDE", "FWD_TILE4", "NO_TMA", "L2HINT",
                                          "CHAINED", "CHUNK_ROWS", "CHAINED_GRID", "CHAINED_HINT", "WAIT_MS", "DEBUG",
-                                         "RESIDENT", "TEST_SKIP_FIRST_CHUNK"};
+                                         "TEST_SKIP_FIRST_CHUNK"};
 constexpr int KNOB_UNSET = INT_MIN;
 
 struct Knobs {
