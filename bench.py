@@ -257,19 +257,43 @@ def measure_host_call(torch, _lib, dev, calls=1000):
         _lib.scan_fwd(t[0], t[1], t[2], t[3], y, tile_h=th)
         _lib.scan_bwd(t[0], t[1], t[2], t[3], t[4], *g, tile_h=th)
 
-    for _ in range(20):
-        pair()
-    torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(calls):
-        pair()
-    host_us = (time.perf_counter() - t0) / calls * 1e6
-    e1.record()
-    torch.cuda.synchronize(dev)
-    return {"host_us_per_fwd_bwd_pair": host_us, "device_us_per_pair": e0.elapsed_time(e1) / calls * 1e3,
-            "shape": [B, L, D], "calls": calls}
+    def time_loop(fn):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(calls):
+            fn()
+        host_us = (time.perf_counter() - t0) / calls * 1e6
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return host_us, e0.elapsed_time(e1) / calls * 1e3
+
+    binding_us, device_us = time_loop(pair)
+
+    # the same two calls straight through the C ABI with the arguments converted once
+    lib = _lib.load()
+    p = [v.data_ptr() for v in t]
+    status = _lib._status_word(dev).data_ptr()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    sb, sl = L * D, D
+    args_f = (p[0], p[1], p[2], p[3], y.data_ptr(), None, th.data_ptr(), None, None, None, 0, B, L, D, sb, sl, sb, sl,
+              _lib.BF16, _lib.BF16, 0, status, stream)
+    args_b = (p[0], p[1], p[2], p[3], p[4], None, th.data_ptr(), None, None, None, *[v.data_ptr() for v in g], None, 0,
+              B, L, D, sb, sl, sb, sl, _lib.BF16, _lib.BF16, 0, status, stream)
+
+    def pair_c():
+        lib.qssm_scan_fwd(*args_f)
+        lib.qssm_scan_bwd(*args_b)
+
+    c_abi_us, _ = time_loop(pair_c)
+    return {"host_us_per_fwd_bwd_pair": binding_us, "c_abi_host_us_per_pair": c_abi_us,
+            "device_us_per_pair": device_us, "shape": [B, L, D], "calls": calls,
+            "note": "host_us: through quick_ssm_b200._lib (argument checks, current stream, ctypes); c_abi: "
+                    "ctypes straight into qssm_scan_fwd + qssm_scan_bwd with prepared arguments; device_us: the "
+                    "same loop's device time per pair (two launches)"}
 
 
 def _strip_check(np, strips, ref_fn):
@@ -305,54 +329,64 @@ def measure_seq_sharded(torch, dist, _lib, dev, rank, world, steps, sync, peak):
     tile_h = torch.empty((B, (Ls + _lib.tile_rows() - 1) // _lib.tile_rows(), D), dtype=torch.float32, device=dev)
     grads = [torch.empty_like(x) for _ in range(4)]
 
-    if world == 1:
-        def fwd(marks=None):
-            _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h)
+    def timed(ops, comm):
+        """Per-rank table [total, fwd, bwd, 3 forward phases, 3 backward phases] in ms per step."""
+        if world == 1:
+            def fwd(marks=None):
+                _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h)
 
-        def bwd(marks=None):
-            _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h)
-    else:
-        ops = sharded.CudaShardOps()
-        comm = sharded.TorchComm(None)
+            def bwd(marks=None):
+                _lib.scan_bwd(x, a, b, c, dy, *grads, tile_h=tile_h)
+        else:
+            def fwd(marks=None):
+                sharded.shard_forward(ops, comm, x, a, b, c, dtype, True, y=y, tile_h=tile_h, marks=marks)
 
-        def fwd(marks=None):
-            sharded.shard_forward(ops, comm, x, a, b, c, dtype, True, y=y, tile_h=tile_h, marks=marks)
+            def bwd(marks=None):
+                sharded.shard_backward(ops, comm, x, a, b, c, dy, tile_h, grads=grads, marks=marks)
 
-        def bwd(marks=None):
-            sharded.shard_backward(ops, comm, x, a, b, c, dy, tile_h, grads=grads, marks=marks)
+        for _ in range(3):
+            fwd()
+            bwd()
+        sync()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+        marks_f, marks_b = [], []
+        ev[0].record()
+        for k in range(steps):
+            fwd(marks_f if world > 1 else None)
+            ev[2 * k + 1].record()
+            bwd(marks_b if world > 1 else None)
+            ev[2 * k + 2].record()
+        sync()
+        _lib.check_device_status(dev)
+        total_ms = ev[0].elapsed_time(ev[-1]) / steps
+        fwd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
+        bwd_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
 
-    for _ in range(3):
-        fwd()
-        bwd()
-    sync()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
-    marks_f, marks_b = [], []
-    ev[0].record()
-    for k in range(steps):
-        fwd(marks_f if world > 1 else None)
-        ev[2 * k + 1].record()
-        bwd(marks_b if world > 1 else None)
-        ev[2 * k + 2].record()
-    sync()
-    _lib.check_device_status(dev)
-    total_ms = ev[0].elapsed_time(ev[-1]) / steps
-    fwd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
-    bwd_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
+        def phases(marks):  # mean ms of (aggregate, exchange + fold, seeded scan)
+            if not marks:
+                return [0.0, 0.0, 0.0]
+            k = len(marks) // 4
+            return [sum(marks[4 * i + j].elapsed_time(marks[4 * i + j + 1]) for i in range(k)) / k for j in range(3)]
 
-    def phases(marks):  # mean ms of (aggregate, all-gather + fold, seeded scan)
-        if not marks:
-            return [0.0, 0.0, 0.0]
-        k = len(marks) // 4
-        return [sum(marks[4 * i + j].elapsed_time(marks[4 * i + j + 1]) for i in range(k)) / k for j in range(3)]
+        mine = torch.tensor([total_ms, fwd_ms, bwd_ms] + phases(marks_f) + phases(marks_b), device=dev,
+                            dtype=torch.float64)
+        if world > 1:
+            allr = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            return torch.stack(allr).cpu()
+        return mine.cpu()[None]
 
-    mine = torch.tensor([total_ms, fwd_ms, bwd_ms] + phases(marks_f) + phases(marks_b), device=dev,
-                        dtype=torch.float64)
-    if world > 1:
-        allr = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(allr, mine)
-        table = torch.stack(allr).cpu()
-    else:
-        table = mine.cpu()[None]
+    comm = sharded.TorchComm(None) if world > 1 else None
+    # the same step with the carries pushed into the peers' inboxes instead of the all-gather: timed
+    # first, so that the results checked below are those of the all-gather path
+    peer_table, peer_note = None, None
+    if world > 1 and not os.environ.get("QSSM_BENCH_NO_PEER"):
+        try:
+            peer = sharded.PeerCarryExchange(None, B * D, dev)
+            peer_table = timed(sharded.CudaShardOps(peer=peer), comm)
+        except Exception as e:  # symmetric memory unavailable on this box: the all-gather path stands alone
+            peer_note = f"{type(e).__name__}: {e}"[:200]
+    table = timed(sharded.CudaShardOps() if world > 1 else None, comm)
 
     # ---- one 64-channel strip, whole sequence, against the oracle (outside the timed region) ----
     d0 = (D // 2 // 64) * 64
@@ -401,6 +435,17 @@ def measure_seq_sharded(torch, dist, _lib, dev, rank, world, steps, sync, peak):
         out["fwd_phases_per_rank"] = {n: [float(v) for v in table[:, 3 + j]] for j, n in enumerate(names)}
         out["bwd_phases_per_rank"] = {n: [float(v) for v in table[:, 6 + j]] for j, n in enumerate(names)}
         out["collective"] = "one NCCL all_gather_into_tensor of 2*B*D fp32 per rank and direction (16 KB per rank)"
+        if peer_table is not None:
+            tp = float(peer_table[:, 0].max())
+            out["peer_exchange"] = {
+                "what": "same step, carries stored into every rank's inbox through peer memory (plain stores over "
+                        "NVLink + flag, bounded-wait fold) instead of the all-gather",
+                "value": n_total / (tp * 1e-3) / 1e9, "ms_per_step": tp,
+                "frac_of_20s_bytes": n_total * 20 * es / (tp * 1e-3) / 1e9 / (world * peak),
+                "fwd_exchange_fold_ms_per_rank": [float(v) for v in peer_table[:, 4]],
+                "bwd_exchange_fold_ms_per_rank": [float(v) for v in peer_table[:, 7]]}
+        elif peer_note is not None:
+            out["peer_exchange"] = {"unavailable": peer_note}
         out["gpu_launches_per_step"] = "fwd: aggregate + segment carry + fold + scan; bwd: the same"
     return out
 

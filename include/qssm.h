@@ -13,8 +13,10 @@
  *     steps); the D stride is 1;
  *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
  *   - the library allocates no device memory, never synchronises and keeps no
- *     state between calls; scratch comes from the caller (`ws`, sized by
- *     qssm_workspace_bytes);
+ *     state between calls that a result depends on (it remembers, per host thread,
+ *     the tensor-map encodings of the buffers it saw last and, per device, what it
+ *     asked the runtime about its own kernels); scratch comes from the caller
+ *     (`ws`, sized by qssm_workspace_bytes);
  *   - return value: 0 ok; < 0 bad argument (QSSM_E_*); > 0 a cudaError_t from
  *     a launch.  Errors found on the device while a kernel runs (a bounded
  *     wait that expired) are reported through `status_word`, an int the
@@ -253,6 +255,44 @@ int qssm_scan_aggregate_bwd(const void* a, const void* c, const void* dy,
 int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k,
                     int64_t n_chan, int64_t upto, int reverse,
                     const float* seed, float* carry, void* stream);
+
+/*
+ * Carry exchange between sequence shards through peer memory, in place of the all-gather followed
+ * by qssm_carry_fold.  No counterpart in the reference (it runs on one GPU).
+ *
+ * Every rank owns, in its own device memory, an inbox of qssm_peer_inbox_bytes(world, n_chan) bytes,
+ * zero before the first call: QSSM_PEER_SLOTS * world * 2 * n_chan floats of aggregate pairs, then
+ * (at qssm_peer_flags_offset) QSSM_PEER_SLOTS * world ints of flags.  Every rank has the inboxes of
+ * all ranks mapped so that its OWN device may store into them (a cuMemCreate allocation shared as a
+ * handle and mapped with cuMemSetAccess for the storing device, e.g. torch's symmetric memory;
+ * `peer_inbox[rank]` is the rank's own inbox).  Only plain loads and stores touch peer memory: no
+ * bulk-copy engine, no multicast.
+ *   qssm_carry_push     : copies this rank's pair (first, second), n_chan floats each, into slot
+ *                         `slot` of every rank's inbox and then sets this rank's flag there to
+ *                         `epoch`.  counters: `world` zeroed unsigned ints in local memory.
+ *   qssm_carry_wait_fold: waits (at most wait_ms, then QSSM_S_TMA_TIMEOUT in *status_word and an
+ *                         unchanged `carry`) until the flags of all ranks in slot `slot` of the local
+ *                         inbox show `epoch`, then carry[c] = the pairs of the ranks before `rank`
+ *                         (reverse != 0: after) folded in rank order onto seed[c] (seed NULL = 0)
+ *                         with (aL,xL)+(aR,xR) = (aR*aL, aR*xL+xR), exactly as qssm_carry_fold does
+ *                         on gathered pairs.
+ * Callers use epoch = 1, 2, 3, ... per direction and slot = 2*direction + (epoch & 1); all ranks
+ * make the same sequence of calls on one stream each.  world <= QSSM_MAX_PEERS.
+ */
+#define QSSM_MAX_PEERS 16
+#define QSSM_PEER_SLOTS 4
+
+size_t qssm_peer_inbox_bytes(int world, int64_t n_chan);
+size_t qssm_peer_flags_offset(int world, int64_t n_chan);
+
+int qssm_carry_push(const float* first, const float* second, int64_t n_chan,
+                    void* const* peer_inbox, unsigned int* counters,
+                    int rank, int world, int slot, int epoch, void* stream);
+
+int qssm_carry_wait_fold(const void* inbox, int64_t n_chan,
+                         int rank, int world, int slot, int epoch, int reverse,
+                         const float* seed, float* carry, int wait_ms,
+                         int* status_word, void* stream);
 
 /*
  * RMS normalisation of the layer input, the step before the projections that feed the scan

@@ -46,6 +46,10 @@ SIGNATURES = {
     "qssm_scan_aggregate_bwd": (_c_int, [_c_vp] * 3 + [_c_vp] * 2 + [_c_vp, _c_sz] + [_c_i64] * 3 + [_c_i64] * 4
                                 + [_c_int] * 3 + [_c_vp, _c_vp]),
     "qssm_carry_fold": (_c_int, [_c_vp, _c_vp, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_vp, _c_vp, _c_vp]),
+    "qssm_peer_inbox_bytes": (_c_sz, [_c_int, _c_i64]),
+    "qssm_peer_flags_offset": (_c_sz, [_c_int, _c_i64]),
+    "qssm_carry_push": (_c_int, [_c_vp, _c_vp, _c_i64, _c_vp, _c_vp] + [_c_int] * 4 + [_c_vp]),
+    "qssm_carry_wait_fold": (_c_int, [_c_vp, _c_i64] + [_c_int] * 5 + [_c_vp, _c_vp, _c_int, _c_vp, _c_vp]),
     "qssm_rmsnorm_workspace_bytes": (_c_sz, [_c_i64]),
     "qssm_rmsnorm_fwd": (_c_int, [_c_vp] * 4 + [_c_i64] * 4 + [ctypes.c_float, _c_int, _c_vp]),
     "qssm_rmsnorm_bwd": (_c_int, [_c_vp] * 6 + [_c_vp, _c_sz] + [_c_i64] * 5 + [_c_int, _c_vp]),
@@ -103,28 +107,40 @@ def dtype_code(dt: torch.dtype) -> int:
 # ---------------------------------------------------------------------------------------------
 # device status word: pinned host memory the kernels can write, read by the host without a sync
 # ---------------------------------------------------------------------------------------------
-_status_words = {}
+_status_words = {}   # device index -> (pinned tensor, its address, a ctypes view of the int)
+
+
+def _status_entry(index: int):
+    e = _status_words.get(index)
+    if e is None:
+        w = torch.zeros(1, dtype=torch.int32).pin_memory()
+        e = _status_words[index] = (w, w.data_ptr(), ctypes.c_int.from_address(w.data_ptr()))
+    return e
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    w = _status_words.get(key)
-    if w is None:
-        w = torch.zeros(1, dtype=torch.int32).pin_memory()
-        _status_words[key] = w
-    return w
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return _status_entry(index)[0]
+
+
+def _raise_status(entry) -> None:
+    code = entry[2].value
+    entry[2].value = 0
+    raise RuntimeError(f"qssm device error {code}: {status_string(code)}")
 
 
 def check_device_status(device: Optional[torch.device] = None, synchronize: bool = False) -> None:
     """Raise if a kernel launched earlier reported a device-side error (e.g. an expired wait)."""
     if synchronize:
         torch.cuda.synchronize(device)
-    words = _status_words.values() if device is None else [_status_word(torch.device(device))]
-    for w in words:
-        code = int(w[0])
-        if code != 0:
-            w.zero_()
-            raise RuntimeError(f"qssm device error {code}: {status_string(code)}")
+    if device is None:
+        entries = list(_status_words.values())
+    else:
+        device = torch.device(device)
+        entries = [_status_entry(device.index if device.index is not None else torch.cuda.current_device())]
+    for e in entries:
+        if e[2].value != 0:
+            _raise_status(e)
 
 
 def _rc(code: int, what: str) -> None:
@@ -140,16 +156,49 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+class _on_device:
+    """``with _on_device(dev)``: make ``dev`` current for the call; free when it already is."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, device: torch.device):
+        self.index = device.index
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.index is None or cur == self.index:
+            self.prev = None
+        else:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def _begin(dev: torch.device):
+    """Per-call prologue: surface an earlier device-side error, return the status word's address."""
+    if _lib is None:
+        load()
+    e = _status_entry(dev.index if dev.index is not None else torch.cuda.current_device())
+    if e[2].value != 0:
+        _raise_status(e)
+    return e[1]
+
+
 def _require_cuda(*tensors) -> torch.device:
     dev = None
     for t in tensors:
         if t is None:
             continue
-        if t.device.type != "cuda":
+        d = t.device
+        if d.type != "cuda":
             raise RuntimeError("the qssm kernels need CUDA tensors; there is no CPU path")
         if dev is None:
-            dev = t.device
-        elif t.device != dev:
+            dev = d
+        elif d != dev:
             raise RuntimeError("all tensors must live on the same CUDA device")
     return dev
 
@@ -172,12 +221,19 @@ def same_layout(*ts: torch.Tensor) -> bool:
     return all(t.stride() == s0 for t in ts[1:])
 
 
+_ws_bytes = {}   # (B, L, D, dtype code) -> bytes the library wants when it picks the segments itself
+
+
 def workspace(B: int, L: int, D: int, code: int, n_seg: int, device) -> Optional[torch.Tensor]:
-    lib = load()
     if n_seg and n_seg > 1:
         nbytes = 3 * B * n_seg * D * 4
     else:
-        nbytes = int(lib.qssm_workspace_bytes(B, L, D, code))
+        key = (B, L, D, code)
+        nbytes = _ws_bytes.get(key)
+        if nbytes is None:
+            if len(_ws_bytes) > 4096:
+                _ws_bytes.clear()
+            nbytes = _ws_bytes[key] = int(load().qssm_workspace_bytes(B, L, D, code))
     if nbytes == 0:
         return None
     return torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -190,18 +246,19 @@ def scan_fwd(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None
     """``n_seg`` < 0 with ``ws`` from ``aggregate_fwd``: reuse the segment aggregates already in ``ws``."""
     dev = _require_cuda(x, a, b, c, y, h_saved, tile_h, h_in, h_last, ws)
     B, L, D = x.shape
-    check_device_status(dev)
-    with torch.cuda.device(dev):
-        code_in, code_out = dtype_code(x.dtype), dtype_code(y.dtype)
+    status = _begin(dev)
+    with _on_device(dev):
+        code_in, code_out = _DTYPE_CODE.get(x.dtype), _DTYPE_CODE.get(y.dtype)
+        if code_in is None or code_out is None:
+            dtype_code(x.dtype), dtype_code(y.dtype)
         if ws is None:
             ws = workspace(B, L, D, code_in, abs(n_seg), dev)
-        sb, sl = _blds(x)
-        ob, ol = _blds(y)
-        rc = load().qssm_scan_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(y), _ptr(h_saved), _ptr(tile_h),
-                                  _ptr(h_in), _ptr(h_last), _ptr(ws), 0 if ws is None else ws.numel(),
-                                  B, L, D, sb, sl, ob, ol, code_in, code_out, int(n_seg),
-                                  _status_word(dev).data_ptr(), _stream(dev))
-    _rc(rc, "qssm_scan_fwd")
+        rc = _lib.qssm_scan_fwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(y), _ptr(h_saved), _ptr(tile_h),
+                                _ptr(h_in), _ptr(h_last), _ptr(ws), 0 if ws is None else ws.numel(),
+                                B, L, D, x.stride(0), x.stride(1), y.stride(0), y.stride(1), code_in, code_out,
+                                n_seg, status, _stream(dev))
+    if rc != 0:
+        _rc(rc, "qssm_scan_fwd")
 
 
 def scan_fwd_static_ws(x, a, b, c, y, *, h_saved=None, tile_h=None, h_in=None, h_last=None, n_seg: int = 0) -> None:
@@ -229,18 +286,19 @@ def scan_bwd(x, a, b, c, dy, dx, da, db, dc, *, h_saved=None, tile_h=None, h_in=
     """``n_seg`` < 0 with ``ws`` from ``aggregate_bwd``: reuse the segment aggregates already in ``ws``."""
     dev = _require_cuda(x, a, b, c, dy, dx, da, db, dc, h_saved, tile_h, h_in, g_in, g_first, ws)
     B, L, D = x.shape
-    check_device_status(dev)
-    with torch.cuda.device(dev):
-        code_in, code_out = dtype_code(x.dtype), dtype_code(dy.dtype)
+    status = _begin(dev)
+    with _on_device(dev):
+        code_in, code_out = _DTYPE_CODE.get(x.dtype), _DTYPE_CODE.get(dy.dtype)
+        if code_in is None or code_out is None:
+            dtype_code(x.dtype), dtype_code(dy.dtype)
         if ws is None:
             ws = workspace(B, L, D, code_in, abs(n_seg), dev)
-        sb, sl = _blds(x)
-        gb, gl = _blds(dy)
-        rc = load().qssm_scan_bwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(dy), _ptr(h_saved), _ptr(tile_h),
-                                  _ptr(h_in), _ptr(g_in), _ptr(g_first), _ptr(dx), _ptr(da), _ptr(db), _ptr(dc),
-                                  _ptr(ws), 0 if ws is None else ws.numel(), B, L, D, sb, sl, gb, gl,
-                                  code_in, code_out, int(n_seg), _status_word(dev).data_ptr(), _stream(dev))
-    _rc(rc, "qssm_scan_bwd")
+        rc = _lib.qssm_scan_bwd(_ptr(x), _ptr(a), _ptr(b), _ptr(c), _ptr(dy), _ptr(h_saved), _ptr(tile_h),
+                                _ptr(h_in), _ptr(g_in), _ptr(g_first), _ptr(dx), _ptr(da), _ptr(db), _ptr(dc),
+                                _ptr(ws), 0 if ws is None else ws.numel(), B, L, D, x.stride(0), x.stride(1),
+                                dy.stride(0), dy.stride(1), code_in, code_out, n_seg, status, _stream(dev))
+    if rc != 0:
+        _rc(rc, "qssm_scan_bwd")
 
 
 class Unsupported(RuntimeError):
@@ -369,3 +427,34 @@ def rmsnorm_bwd(x, w, dy, rstd, dx, dw) -> None:
     if rc in (-3, -4):
         raise Unsupported(status_string(rc))
     _rc(rc, "qssm_rmsnorm_bwd")
+
+
+MAX_PEERS, PEER_SLOTS = 16, 4
+
+
+def peer_inbox_bytes(world: int, n_chan: int) -> int:
+    return int(load().qssm_peer_inbox_bytes(int(world), int(n_chan)))
+
+
+def carry_push(first, second, inbox_ptrs, counters, rank: int, slot: int, epoch: int) -> None:
+    """Store this rank's aggregate pair into slot ``slot`` of every rank's inbox (device pointers as
+    ints, own rank included) and publish ``epoch`` in this rank's flag there."""
+    dev = _require_cuda(first, second, counters)
+    world = len(inbox_ptrs)
+    arr_t = ctypes.c_void_p * world
+    with _on_device(dev):
+        rc = load().qssm_carry_push(_ptr(first), _ptr(second), first.numel(), arr_t(*inbox_ptrs), _ptr(counters),
+                                    rank, world, slot, epoch, _stream(dev))
+    _rc(rc, "qssm_carry_push")
+
+
+def carry_wait_fold(inbox_ptr: int, n_chan: int, rank: int, world: int, slot: int, epoch: int, reverse: bool,
+                    carry, seed=None, wait_ms: int = 2000) -> None:
+    """Wait (bounded) until every rank's pair of this call has arrived in the local inbox, then fold
+    the pairs of the ranks this one depends on."""
+    dev = _require_cuda(carry, seed)
+    status = _begin(dev)
+    with _on_device(dev):
+        rc = load().qssm_carry_wait_fold(inbox_ptr, n_chan, rank, world, slot, epoch, 1 if reverse else 0,
+                                         _ptr(seed), _ptr(carry), int(wait_ms), status, _stream(dev))
+    _rc(rc, "qssm_carry_wait_fold")

@@ -54,6 +54,7 @@
 #include "qssm_fwd.cuh"
 #include "qssm_gated.cuh"
 #include "qssm_norm.cuh"
+#include "qssm_peer.cuh"
 
 using namespace qssm;
 
@@ -142,6 +143,32 @@ inline int knob(Knob k, int dflt) {
     return v == KNOB_UNSET ? dflt : v;
 }
 
+// A tensor map is a pure function of (base, dtype, extents, pitches, box).  Training loops call with the
+// same buffers step after step (a caching allocator hands the same addresses back), so each host thread
+// keeps the maps it encoded last: a hit copies 128 bytes instead of calling into the driver.
+struct MapKey {
+    const void* ptr;
+    long long B, rows, D, sb, sl;
+    int dt, box_d, box_rows, pad;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && B == o.B && rows == o.rows && D == o.D && sb == o.sb && sl == o.sl && dt == o.dt &&
+               box_d == o.box_d && box_rows == o.box_rows;
+    }
+};
+struct MapCache {
+    static constexpr int N = 64;  // direct mapped
+    MapKey key[N];
+    CUtensorMap map[N];
+    bool used[N];
+    MapCache() { memset(used, 0, sizeof(used)); }
+    static unsigned slot_of(const MapKey& k) {
+        unsigned long long h = (unsigned long long)reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (unsigned long long)k.box_d * 0x85EBCA6Bull + (unsigned long long)k.box_rows * 0xC2B2AE35ull +
+             (unsigned long long)k.rows * 0x27D4EB2Full + (unsigned long long)k.dt;
+        return (unsigned)(h >> 40) % N;
+    }
+};
+
 // dims (D, rows, B); box (box_d, box_rows, 1)
 int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long rows, long long D, long long sb,
               long long sl, int box_d, int box_rows, bool use_tma) {
@@ -150,6 +177,13 @@ int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long ro
     td.stride_b = sb;
     td.stride_l = sl;
     if (!use_tma || ptr == nullptr) return 0;
+    static thread_local MapCache cache;
+    const MapKey key{ptr, B, rows, D, sb, sl, dt, box_d, box_rows, 0};
+    const unsigned slot = MapCache::slot_of(key);
+    if (cache.used[slot] && cache.key[slot] == key) {
+        td.map = cache.map[slot];
+        return 0;
+    }
     static thread_local bool have_context = false;
     if (!have_context) {
         ensure_context();
@@ -175,7 +209,11 @@ int fill_desc(TensorDesc& td, const void* ptr, int dt, long long B, long long ro
                 (int)r, ptr, dt, (unsigned long long)dims[0], (unsigned long long)dims[1],
                 (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box[0],
                 box[1], box[2]);
-    return r == CUDA_SUCCESS ? 0 : QSSM_E_STRIDE;
+    if (r != CUDA_SUCCESS) return QSSM_E_STRIDE;
+    cache.key[slot] = key;
+    cache.map[slot] = td.map;
+    cache.used[slot] = true;
+    return 0;
 }
 
 constexpr int MAX_DEVICES = 64;
@@ -1362,6 +1400,62 @@ int qssm_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float*
             return (int)cudaGetLastError();
         }
     });
+}
+
+// ---------------------------------------------------------------------------------------------
+// carry exchange through peer memory
+// ---------------------------------------------------------------------------------------------
+static_assert(QSSM_MAX_PEERS == MAX_PEERS && QSSM_PEER_SLOTS == PEER_SLOTS, "header and kernels disagree");
+
+size_t qssm_peer_inbox_bytes(int world, int64_t n_chan) {
+    if (world < 1 || n_chan < 0) return 0;
+    const size_t data = (size_t)PEER_SLOTS * (size_t)world * 2 * (size_t)n_chan * sizeof(float);
+    return ((data + 255) / 256) * 256 + (size_t)PEER_SLOTS * (size_t)world * sizeof(int);
+}
+
+size_t qssm_peer_flags_offset(int world, int64_t n_chan) {
+    if (world < 1 || n_chan < 0) return 0;
+    const size_t data = (size_t)PEER_SLOTS * (size_t)world * 2 * (size_t)n_chan * sizeof(float);
+    return ((data + 255) / 256) * 256;
+}
+
+int qssm_carry_push(const float* first, const float* second, int64_t n_chan, void* const* peer_inbox,
+                    unsigned int* counters, int rank, int world, int slot, int epoch, void* stream) {
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || slot < 0 || slot >= PEER_SLOTS || n_chan < 0)
+        return QSSM_E_SHAPE;
+    if (n_chan == 0) return 0;
+    if (first == nullptr || second == nullptr || peer_inbox == nullptr || counters == nullptr) return QSSM_E_NULL;
+    PeerPushParams p;
+    memset(&p, 0, sizeof(p));
+    p.first = first; p.second = second; p.counters = counters; p.n_chan = n_chan;
+    p.rank = rank; p.world = world; p.slot = slot; p.epoch = epoch;
+    const size_t flags_off = qssm_peer_flags_offset(world, n_chan);
+    for (int k = 0; k < world; ++k) {
+        if (peer_inbox[k] == nullptr) return QSSM_E_NULL;
+        p.inbox[k] = static_cast<float*>(peer_inbox[k]);
+        p.flags[k] = reinterpret_cast<int*>(static_cast<unsigned char*>(peer_inbox[k]) + flags_off);
+    }
+    long long per_peer = (n_chan + 1023) / 1024;  // about four elements of each array per thread
+    if (per_peer > 32) per_peer = 32;
+    carry_push_kernel<<<dim3((unsigned)per_peer, (unsigned)world), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return (int)cudaGetLastError();
+}
+
+int qssm_carry_wait_fold(const void* inbox, int64_t n_chan, int rank, int world, int slot, int epoch, int reverse,
+                         const float* seed, float* carry, int wait_ms, int* status_word, void* stream) {
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || slot < 0 || slot >= PEER_SLOTS || n_chan < 0)
+        return QSSM_E_SHAPE;
+    if (n_chan == 0) return 0;
+    if (inbox == nullptr || carry == nullptr) return QSSM_E_NULL;
+    long long grid = (n_chan + 255) / 256;
+    if (grid > 2ll * sm_count()) grid = 2ll * sm_count();
+    const unsigned long long wait_ns = (unsigned long long)(wait_ms < 1 ? 1 : wait_ms) * 1000000ull;
+    const int* flags = reinterpret_cast<const int*>(static_cast<const unsigned char*>(inbox) +
+                                                    qssm_peer_flags_offset(world, n_chan));
+    carry_wait_fold_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float*>(inbox), flags, n_chan, rank, world, slot, epoch, reverse, seed, carry, wait_ns,
+        status_word);
+    return (int)cudaGetLastError();
 }
 
 }  // extern "C"

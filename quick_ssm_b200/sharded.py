@@ -31,7 +31,8 @@ class CudaShardOps:
     per-segment aggregates in a workspace that the scan call right after it reuses, so the
     tensors the carry depends on are read once for both purposes."""
 
-    def __init__(self):
+    def __init__(self, peer: Optional["PeerCarryExchange"] = None):
+        self.peer = peer     # carry exchange through peer memory instead of an all-gather (optional)
         self._ws_fwd = None  # (workspace, segments) left by aggregate_fwd for the next forward
         self._ws_bwd = None
         self._ws_cache = {}
@@ -127,6 +128,64 @@ class Exchange:
         return self.full[:, 0], self.full[:, 1]
 
 
+class PeerCarryExchange:
+    """Carry exchange of sequence shards through peer memory instead of an all-gather.
+
+    Every rank allocates an inbox (aggregate pairs of all ranks, four slots, and their flags) from
+    torch's symmetric memory: a ``cuMemCreate`` allocation whose handle the ranks of ``group`` (all
+    on one node) exchange and map with access for their OWN device, so a kernel on this rank's GPU
+    may store into any rank's inbox over NVLink.  ``carry_in`` then is two small kernels on the calling stream: ``qssm_carry_push`` stores this rank's pair into
+    every inbox and raises its flag there; ``qssm_carry_wait_fold`` waits - bounded - for every
+    rank's pair and folds those it depends on in rank order, the same arithmetic as
+    ``qssm_carry_fold`` on gathered pairs, so results are bit-identical to the all-gather path.
+    No collective, no host synchronisation, no multicast, no bulk copies on peer memory.  All ranks
+    must call ``carry_in`` the same number of times per direction.
+    """
+
+    def __init__(self, group, n_chan: int, device, wait_ms: int = 2000):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all it needs
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"at most {_lib.MAX_PEERS} ranks")
+        self.n_chan, self.wait_ms = int(n_chan), int(wait_ms)
+        self.device = torch.device(device)
+        nbytes = _lib.peer_inbox_bytes(self.world, self.n_chan)
+        self.inbox = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.inbox.zero_()
+        self._handle = symm_mem.rendezvous(self.inbox, group)
+        self.inbox_ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        if self.inbox_ptrs[self.rank] != self.inbox.data_ptr():
+            raise RuntimeError("symmetric memory: the local buffer is not at its own mapping")
+        self.counters = torch.zeros(max(self.world, 32), dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)  # every inbox is zeroed and mapped before the first push
+        self.epoch = [0, 0]  # per direction
+
+    def carry_in(self, first: torch.Tensor, second: torch.Tensor, reverse: bool) -> torch.Tensor:
+        d = 1 if reverse else 0
+        self.epoch[d] += 1
+        epoch = self.epoch[d]
+        slot = 2 * d + (epoch & 1)
+        carry = torch.empty_like(first)
+        _lib.carry_push(first, second, self.inbox_ptrs, self.counters, self.rank, slot, epoch)
+        _lib.carry_wait_fold(self.inbox_ptrs[self.rank], self.n_chan, self.rank, self.world, slot, epoch, reverse,
+                             carry, wait_ms=self.wait_ms)
+        return carry
+
+
+def _carry_in(ops, comm, ex: "Exchange", reverse: bool):
+    """State entering this rank's shard: through the peer exchange when the ops carry one, else one
+    all-gather and a fold."""
+    peer = getattr(ops, "peer", None)
+    if peer is not None:
+        return peer.carry_in(ex.send[0], ex.send[1], reverse)
+    first_all, second_all = ex.gather()
+    return ops.fold(first_all, second_all, comm.rank, reverse)
+
+
 def forward_aggregate(ops, comm, xs, as_, bs) -> Exchange:
     """First half of a shard's forward: its aggregate, written into the send buffer of the exchange."""
     B, L, D = xs.shape
@@ -140,8 +199,7 @@ def forward_aggregate(ops, comm, xs, as_, bs) -> Exchange:
 
 def forward_finish(ops, comm, ex: Exchange, xs, as_, bs, cs, y, tile_h, mark=lambda: None):
     """Second half: all-gather, fold the shards before this one into ``h_in``, seeded scan."""
-    A_all, H_all = ex.gather()
-    h_in = ops.fold(A_all, H_all, comm.rank, False)
+    h_in = _carry_in(ops, comm, ex, False)
     mark()
     ops.forward(xs, as_, bs, cs, y, tile_h, h_in)
 
@@ -157,8 +215,7 @@ def backward_aggregate(ops, comm, as_, cs, dy) -> Exchange:
 
 
 def backward_finish(ops, comm, ex: Exchange, xs, as_, bs, cs, dy, tile_h, grads, mark=lambda: None):
-    P_all, Q_all = ex.gather()
-    g_in = ops.fold(P_all, Q_all, comm.rank, True)
+    g_in = _carry_in(ops, comm, ex, True)
     mark()
     ops.backward(xs, as_, bs, cs, dy, tile_h, g_in, grads)
 

@@ -85,8 +85,9 @@ def test_layer_runs_on_cpu_with_torch_backend():
 
 
 def test_status_word_raises_once_and_clears():
+    import ctypes
     w = torch.zeros(1, dtype=torch.int32)
-    _lib._status_words[99] = w
+    _lib._status_words[99] = (w, w.data_ptr(), ctypes.c_int.from_address(w.data_ptr()))
     try:
         w[0] = 10001
         with pytest.raises(RuntimeError, match="expired"):
