@@ -103,8 +103,19 @@ def run_norm(args):
         fused = _median_ms(lambda: step(rms_norm), args.steps, args.warmup, torch.cuda.synchronize)
         composed = _median_ms(lambda: step(_composed), args.steps, args.warmup, torch.cuda.synchronize)
         s = x.element_size()
+        # the kernels alone, through the C ABI on preallocated tensors (no autograd, no allocations)
+        xd, w32 = x.detach(), w.detach().float()
+        y, dx, dw = torch.empty_like(xd), torch.empty_like(xd), torch.empty_like(w32)
+        rstd = torch.empty(B * L, dtype=torch.float32, device=dev)
+        k_fwd = _median_ms(lambda: _lib.rmsnorm_fwd(xd, w32, y, rstd, 1e-5), args.steps, args.warmup,
+                           torch.cuda.synchronize)
+        k_bwd = _median_ms(lambda: _lib.rmsnorm_bwd(xd, w32, dy, rstd, dx, dw), args.steps, args.warmup,
+                           torch.cuda.synchronize)
+        n = B * L * H
         out[name] = {"fused_ms": round(fused, 4), "torch_ms": round(composed, 4), "speedup": round(composed / fused, 2),
-                     "fused_gbs_of_5s_bytes": B * L * H * 5 * s / (fused * 1e-3) / 1e9}
+                     "fused_gbs_of_5s_bytes": n * 5 * s / (fused * 1e-3) / 1e9,
+                     "kernel_fwd_ms": round(k_fwd, 4), "kernel_fwd_gbs_of_2s_bytes": n * 2 * s / (k_fwd * 1e-3) / 1e9,
+                     "kernel_bwd_ms": round(k_bwd, 4), "kernel_bwd_gbs_of_3s_bytes": n * 3 * s / (k_bwd * 1e-3) / 1e9}
     print(json.dumps(out), flush=True)
 
 

@@ -1282,32 +1282,38 @@ int qssm_carry_fold(const float* A, const float* H, int64_t n, int64_t stride_k,
 namespace {
 
 constexpr int NORM_CTAS_PER_SM = 4;  // upper bound used to size the scratch
-constexpr int NORM_FWD_CHUNKS = 32;  // rows of up to 4096 elements stay in registers in the forward,
-constexpr int NORM_BWD_CHUNKS = 16;  // 2048 in the backward (x, w*dy and the dw sums: three values per element)
+constexpr int NORM_FWD_ELEMS = 128;  // elements per lane held in registers: rows of up to 4096 in the forward,
+constexpr int NORM_BWD_ELEMS = 64;   // 2048 in the backward (x, w*dy and the dw sums: three values per element)
 
 int norm_check(const void* a, long long stride, long long H, int es) {
     const long long align = es == 4 ? 16 : 8;
     if (reinterpret_cast<uintptr_t>(a) % align != 0 || (stride * es) % align != 0 || stride < H) return QSSM_E_STRIDE;
     return 0;
 }
+// 16-bit rows that can be moved 16 bytes (eight elements) per lane and access
+bool norm_wide_ok(const void* a, long long stride, long long H) {
+    return H % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 && (stride * 2) % 16 == 0;
+}
 
-// calls f(T{}, Int<NCH>{}) for the element type and the number of 128-element chunks held in registers
-// (0 = rows longer than max_chunks chunks: read twice)
-template <typename F> int norm_dispatch(int dtype, long long H, int max_chunks, F&& f) {
-    auto with_type = [&](auto t) -> int {
-        const long long n = (H + 127) / 128;
-        if (n > max_chunks) return f(t, Int<0>{});
-        if (n <= 1) return f(t, Int<1>{});
-        if (n <= 2) return f(t, Int<2>{});
-        if (n <= 4) return f(t, Int<4>{});
-        if (n <= 8) return f(t, Int<8>{});
-        if (n <= 16) return f(t, Int<16>{});
-        return f(t, Int<32>{});
+// calls f(T{}, Int<NCH>{}, Int<EPL>{}) for the element type, the number of 32*EPL-element chunks held in
+// registers (0 = rows longer than the register budget of max_elems elements per lane: read twice) and the
+// elements per lane and access (8 only for 16-bit rows with `wide`)
+template <typename F> int norm_dispatch(int dtype, long long H, int max_elems, bool wide, F&& f) {
+    auto with_type = [&](auto t, auto epl) -> int {
+        constexpr int EPL = decltype(epl)::value;
+        const long long n = (H + 32 * EPL - 1) / (32 * EPL);
+        if (n * EPL > max_elems) return f(t, Int<0>{}, epl);
+        if (n <= 1) return f(t, Int<1>{}, epl);
+        if (n <= 2) return f(t, Int<2>{}, epl);
+        if (n <= 4) return f(t, Int<4>{}, epl);
+        if (n <= 8) return f(t, Int<8>{}, epl);
+        if (n <= 16) return f(t, Int<16>{}, epl);
+        return f(t, Int<32>{}, epl);
     };
     switch (dtype) {
-        case QSSM_F32: return with_type(float{});
-        case QSSM_F16: return with_type(__half{});
-        case QSSM_BF16: return with_type(__nv_bfloat16{});
+        case QSSM_F32: return with_type(float{}, Int<4>{});
+        case QSSM_F16: return wide ? with_type(__half{}, Int<8>{}) : with_type(__half{}, Int<4>{});
+        case QSSM_BF16: return wide ? with_type(__nv_bfloat16{}, Int<8>{}) : with_type(__nv_bfloat16{}, Int<4>{});
         default: return QSSM_E_DTYPE;
     }
 }
@@ -1329,7 +1335,7 @@ extern "C" {
 size_t qssm_rmsnorm_workspace_bytes(int64_t H) {
     if (H <= 0) return 0;
     // one partial row of dw per CTA, or per warp when rows are too long for the backward's registers
-    const size_t parts = (size_t)sm_count() * NORM_CTAS_PER_SM * (H > 128 * NORM_BWD_CHUNKS ? NORM_WARPS : 1);
+    const size_t parts = (size_t)sm_count() * NORM_CTAS_PER_SM * (H > 32 * NORM_BWD_ELEMS ? NORM_WARPS : 1);
     return parts * (size_t)H * 4;
 }
 
@@ -1349,9 +1355,10 @@ int qssm_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, int64_
     memset(&p, 0, sizeof(p));
     p.x = x; p.w = w; p.y = y; p.rstd = rstd;
     p.rows = rows; p.x_stride = x_stride; p.y_stride = y_stride; p.H = (int)H; p.eps = eps;
-    return norm_dispatch(dtype, H, NORM_FWD_CHUNKS, [&](auto t, auto nch) -> int {
+    const bool wide = es == 2 && norm_wide_ok(x, x_stride, H) && norm_wide_ok(y, y_stride, H);
+    return norm_dispatch(dtype, H, NORM_FWD_ELEMS, wide, [&](auto t, auto nch, auto epl) -> int {
         using T = decltype(t);
-        auto kernel = rmsnorm_fwd_kernel<T, decltype(nch)::value>;
+        auto kernel = rmsnorm_fwd_kernel<T, decltype(nch)::value, decltype(epl)::value>;
         const long long grid = norm_grid(kernel, rows, 0);
         if (grid < 1) return QSSM_E_SHAPE;
         kernel<<<(unsigned)grid, 32 * NORM_WARPS, 0, stream>>>(p);
@@ -1382,13 +1389,15 @@ int qssm_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float*
     p.x = x; p.w = w; p.y = dx; p.dy = dy; p.rstd = const_cast<float*>(rstd);
     p.dw_part = static_cast<float*>(ws);
     p.rows = rows; p.x_stride = x_stride; p.y_stride = dx_stride; p.dy_stride = dy_stride; p.H = (int)H;
-    return norm_dispatch(dtype, H, NORM_BWD_CHUNKS, [&](auto t, auto nch) -> int {
+    const bool wide = es == 2 && norm_wide_ok(x, x_stride, H) && norm_wide_ok(dy, dy_stride, H) &&
+                      norm_wide_ok(dx, dx_stride, H);
+    return norm_dispatch(dtype, H, NORM_BWD_ELEMS, wide, [&](auto t, auto nch, auto epl) -> int {
         using T = decltype(t);
-        constexpr int NCH = decltype(nch)::value;
-        if constexpr (NCH > NORM_BWD_CHUNKS) {
+        constexpr int NCH = decltype(nch)::value, EPL = decltype(epl)::value;
+        if constexpr (NCH * EPL > NORM_BWD_ELEMS) {
             return QSSM_E_SHAPE;  // never dispatched: longer rows take NCH = 0
         } else {
-            auto kernel = rmsnorm_bwd_kernel<T, NCH>;
+            auto kernel = rmsnorm_bwd_kernel<T, NCH, EPL>;
             const int smem = NCH > 0 ? (int)H * 4 : 0;
             const long long grid = norm_grid(kernel, rows, smem);
             if (grid < 1) return QSSM_E_SHAPE;

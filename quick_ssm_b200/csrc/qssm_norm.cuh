@@ -9,12 +9,17 @@
 //     r = 1 / sqrt(mean(x^2) + eps)
 //     dx = r * (w*dy) - x * r^3 * mean(x * w*dy)          dw = sum over rows of dy * x * r
 //
-// One warp per row, persistent over rows.  A lane owns the elements [128*c + 4*lane, +4) of every
-// 128-element chunk c (one 16-byte access of fp32, 8 bytes of 16-bit data; a warp reads 512 / 256
-// contiguous bytes).  Rows of up to 128*NCH elements are held in registers between the reduction and
-// the output; longer rows (NCH = 0) are read twice, the second time from L1/L2.
+// One warp per row, persistent over rows.  A lane owns EPL consecutive elements of every chunk of
+// 32*EPL elements: EPL = 4 (one 16-byte access of fp32, 8 bytes of 16-bit data) or, for 16-bit rows
+// whose length and pitch are multiples of 8 elements, EPL = 8 (16 bytes: half the load and store
+// instructions per element, which is what bounds these kernels on 16-bit data).  Rows of up to
+// 32*EPL*NCH elements are held in registers between the reduction and the output; longer rows
+// (NCH = 0) are read twice, the second time from L1/L2.  The forward also keeps the weight in
+// registers across the rows a warp walks (it is read from L1 once per warp instead of once per row).
 // No bulk copies: rows are short, contiguous and touched once; shared memory only for the dw partials.
 #pragma once
+#include <type_traits>
+
 #include "qssm_tile.cuh"
 
 namespace qssm {
@@ -56,6 +61,54 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
     *reinterpret_cast<uint2*>(p) = q;
 }
 
+// EPL elements per lane and access: 4 (16 bytes of fp32, 8 bytes of 16-bit data) or, for 16-bit data whose
+// rows allow it, 8 (16 bytes): half the load/store instructions per element.
+template <typename T, int EPL> __device__ __forceinline__ void loadv(const T* p, float (&v)[EPL]) {
+    if constexpr (EPL == 4) {
+        load4<T>(p, v);
+    } else {
+        static_assert(EPL == 8 && sizeof(T) == 2, "eight elements per access are for 16-bit data");
+        const uint4 q = *reinterpret_cast<const uint4*>(p);
+        const unsigned int w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if constexpr (std::is_same<T, __half>::value) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            } else {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+    }
+}
+template <typename T, int EPL> __device__ __forceinline__ void storev(T* p, const float (&v)[EPL]) {
+    if constexpr (EPL == 4) {
+        store4<T>(p, v);
+    } else {
+        unsigned int w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if constexpr (std::is_same<T, __half>::value) {
+                const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const unsigned int*>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const unsigned int*>(&h);
+            }
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+template <int EPL> __device__ __forceinline__ void loadw(const float* p, float (&v)[EPL]) {
+#pragma unroll
+    for (int i = 0; i < EPL; i += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p + i);
+        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -75,66 +128,87 @@ struct NormParams {
     float eps;
 };
 
-template <typename T, int NCH>
+template <typename T, int NCH, int EPL>
 __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_fwd_kernel(const NormParams p) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
     const long long n_warps = (long long)gridDim.x * NORM_WARPS;
     const int H = p.H;
     const float inv_h = 1.f / (float)H;
+    constexpr bool W_IN_REGS = NCH > 0 && NCH * EPL <= 32;  // up to 32 weights per lane stay in registers
+    float wreg[W_IN_REGS ? NCH : 1][EPL];
+    if (W_IN_REGS) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int col = (c * 32 + lane) * EPL;
+            if (col < H) loadw<EPL>(p.w + col, wreg[c]);
+            else {
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) wreg[c][i] = 0.f;
+            }
+        }
+    }
     for (long long row = warp; row < p.rows; row += n_warps) {
         const T* xr = static_cast<const T*>(p.x) + row * p.x_stride;
         T* yr = static_cast<T*>(p.y) + row * p.y_stride;
         float ss = 0.f;
         if (NCH > 0) {
-            float v[NCH > 0 ? NCH : 1][4];
+            float v[NCH > 0 ? NCH : 1][EPL];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const int col = (c * 32 + lane) * 4;
-                if (col < H) load4<T>(xr + col, v[c]);
-                else v[c][0] = v[c][1] = v[c][2] = v[c][3] = 0.f;
+                const int col = (c * 32 + lane) * EPL;
+                if (col < H) loadv<T, EPL>(xr + col, v[c]);
+                else {
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) v[c][i] = 0.f;
+                }
             }
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) ss = fmaf(v[c][i], v[c][i], ss);
+                for (int i = 0; i < EPL; ++i) ss = fmaf(v[c][i], v[c][i], ss);
             ss = warp_sum(ss);
             const float r = 1.f / sqrtf(ss * inv_h + p.eps);
             if (lane == 0 && p.rstd != nullptr) p.rstd[row] = r;
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const int col = (c * 32 + lane) * 4;
+                const int col = (c * 32 + lane) * EPL;
                 if (col < H) {
-                    float w4[4], o[4];
-                    load4<float>(p.w + col, w4);
+                    float w4[EPL], o[EPL];
+                    if (W_IN_REGS) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] = v[c][i] * (w4[i] * r);
-                    store4<T>(yr + col, o);
+                        for (int i = 0; i < EPL; ++i) w4[i] = wreg[W_IN_REGS ? c : 0][i];
+                    } else {
+                        loadw<EPL>(p.w + col, w4);
+                    }
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) o[i] = v[c][i] * (w4[i] * r);
+                    storev<T, EPL>(yr + col, o);
                 }
             }
         } else {
-            for (int col = lane * 4; col < H; col += 128) {
-                float v[4];
-                load4<T>(xr + col, v);
+            for (int col = lane * EPL; col < H; col += 32 * EPL) {
+                float v[EPL];
+                loadv<T, EPL>(xr + col, v);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) ss = fmaf(v[i], v[i], ss);
+                for (int i = 0; i < EPL; ++i) ss = fmaf(v[i], v[i], ss);
             }
             ss = warp_sum(ss);
             const float r = 1.f / sqrtf(ss * inv_h + p.eps);
             if (lane == 0 && p.rstd != nullptr) p.rstd[row] = r;
-            for (int col = lane * 4; col < H; col += 128) {
-                float v[4], w4[4], o[4];
-                load4<T>(xr + col, v);
-                load4<float>(p.w + col, w4);
+            for (int col = lane * EPL; col < H; col += 32 * EPL) {
+                float v[EPL], w4[EPL], o[EPL];
+                loadv<T, EPL>(xr + col, v);
+                loadw<EPL>(p.w + col, w4);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[i] = v[i] * (w4[i] * r);
-                store4<T>(yr + col, o);
+                for (int i = 0; i < EPL; ++i) o[i] = v[i] * (w4[i] * r);
+                storev<T, EPL>(yr + col, o);
             }
         }
     }
 }
 
-template <typename T, int NCH>
+template <typename T, int NCH, int EPL>
 __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const NormParams p) {
     const int lane = threadIdx.x & 31;
     const long long warp = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
@@ -143,12 +217,17 @@ __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const Norm
     const float inv_h = 1.f / (float)H;
     float* const part = p.dw_part + (NCH > 0 ? (long long)blockIdx.x : warp) * H;  // long rows: one per warp
 
-    float acc[NCH > 0 ? NCH : 1][4];
+    float acc[NCH > 0 ? NCH : 1][EPL];
     if (NCH > 0) {
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) acc[c][i] = 0.f;
     } else {
-        for (int col = lane * 4; col < H; col += 128) *reinterpret_cast<float4*>(part + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int col = lane * EPL; col < H; col += 32 * EPL) {
+#pragma unroll
+            for (int i = 0; i < EPL; i += 4) *reinterpret_cast<float4*>(part + col + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
 
     for (long long row = warp; row < p.rows; row += n_warps) {
@@ -160,26 +239,26 @@ __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const Norm
         if (NCH > 0) {
             // all loads of the row first (they are independent: the whole row is in flight at once), then
             // the arithmetic; wg holds dy on the way in and w*dy afterwards
-            float v[NCH > 0 ? NCH : 1][4], wg[NCH > 0 ? NCH : 1][4];
+            float v[NCH > 0 ? NCH : 1][EPL], wg[NCH > 0 ? NCH : 1][EPL];
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const int col = (c * 32 + lane) * 4;
+                const int col = (c * 32 + lane) * EPL;
                 if (col < H) {
-                    load4<T>(xr + col, v[c]);
-                    load4<T>(gr + col, wg[c]);
+                    loadv<T, EPL>(xr + col, v[c]);
+                    loadv<T, EPL>(gr + col, wg[c]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[c][i] = wg[c][i] = 0.f;
+                    for (int i = 0; i < EPL; ++i) v[c][i] = wg[c][i] = 0.f;
                 }
             }
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const int col = (c * 32 + lane) * 4;
+                const int col = (c * 32 + lane) * EPL;
                 if (col < H) {
-                    float w4[4];
-                    load4<float>(p.w + col, w4);
+                    float w4[EPL];
+                    loadw<EPL>(p.w + col, w4);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < EPL; ++i) {
                         acc[c][i] = fmaf(wg[c][i] * r, v[c][i], acc[c][i]);
                         wg[c][i] *= w4[i];
                         dot = fmaf(v[c][i], wg[c][i], dot);
@@ -190,38 +269,42 @@ __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const Norm
             const float k = dot * inv_h * r * r * r;
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
-                const int col = (c * 32 + lane) * 4;
+                const int col = (c * 32 + lane) * EPL;
                 if (col < H) {
-                    float o[4];
+                    float o[EPL];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] = fmaf(-v[c][i], k, r * wg[c][i]);
-                    store4<T>(dr + col, o);
+                    for (int i = 0; i < EPL; ++i) o[i] = fmaf(-v[c][i], k, r * wg[c][i]);
+                    storev<T, EPL>(dr + col, o);
                 }
             }
         } else {
-            for (int col = lane * 4; col < H; col += 128) {
-                float v[4], g[4], w4[4], a4[4];
-                load4<T>(xr + col, v);
-                load4<T>(gr + col, g);
-                load4<float>(p.w + col, w4);
-                load4<float>(part + col, a4);
+            for (int col = lane * EPL; col < H; col += 32 * EPL) {
+                float v[EPL], g[EPL], w4[EPL], a4[EPL];
+                loadv<T, EPL>(xr + col, v);
+                loadv<T, EPL>(gr + col, g);
+                loadw<EPL>(p.w + col, w4);
+                loadw<EPL>(part + col, a4);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < EPL; ++i) {
                     a4[i] = fmaf(g[i] * r, v[i], a4[i]);
                     dot = fmaf(v[i], w4[i] * g[i], dot);
                 }
-                store4<float>(part + col, a4);
+                {
+#pragma unroll
+                    for (int i = 0; i < EPL; i += 4)
+                        *reinterpret_cast<float4*>(part + col + i) = make_float4(a4[i], a4[i + 1], a4[i + 2], a4[i + 3]);
+                }
             }
             dot = warp_sum(dot);
             const float k = dot * inv_h * r * r * r;
-            for (int col = lane * 4; col < H; col += 128) {
-                float v[4], g[4], w4[4], o[4];
-                load4<T>(xr + col, v);
-                load4<T>(gr + col, g);
-                load4<float>(p.w + col, w4);
+            for (int col = lane * EPL; col < H; col += 32 * EPL) {
+                float v[EPL], g[EPL], w4[EPL], o[EPL];
+                loadv<T, EPL>(xr + col, v);
+                loadv<T, EPL>(gr + col, g);
+                loadw<EPL>(p.w + col, w4);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[i] = fmaf(-v[i], k, r * (w4[i] * g[i]));
-                store4<T>(dr + col, o);
+                for (int i = 0; i < EPL; ++i) o[i] = fmaf(-v[i], k, r * (w4[i] * g[i]));
+                storev<T, EPL>(dr + col, o);
             }
         }
     }
@@ -231,13 +314,17 @@ __global__ void __launch_bounds__(32 * NORM_WARPS) rmsnorm_bwd_kernel(const Norm
             if ((int)(threadIdx.x >> 5) == wv) {
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
-                    const int col = (c * 32 + lane) * 4;
+                    const int col = (c * 32 + lane) * EPL;
                     if (col < H) {
-                        float t[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (wv > 0) load4<float>(red + col, t);
+                        float t[EPL];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) t[i] += acc[c][i];
-                        store4<float>(red + col, t);
+                        for (int i = 0; i < EPL; ++i) t[i] = 0.f;
+                        if (wv > 0) loadw<EPL>(red + col, t);
+#pragma unroll
+                        for (int i = 0; i < EPL; ++i) t[i] += acc[c][i];
+#pragma unroll
+                        for (int i = 0; i < EPL; i += 4)
+                            *reinterpret_cast<float4*>(red + col + i) = make_float4(t[i], t[i + 1], t[i + 2], t[i + 3]);
                     }
                 }
             }
