@@ -65,7 +65,7 @@ int qssm_version(void);
  * Tuning knobs and the test hook.  No counterpart in the reference; production callers use neither.
  * Launch-shape choices (strip width "V", tile rows "TB", ring depth "STAGES", "NOUT", "GRID", "WIDE",
  * "FWD_TILE4", "NO_TMA", "L2HINT", the single-pass kernels "CHAINED", "CHUNK_ROWS", "CHAINED_GRID",
- * "CHAINED_HINT", the limit of bounded waits "WAIT_MS", "DEBUG") take their values from the
+ * "CHAINED_HINT", "CHAINED_SLOTS", the limit of bounded waits "WAIT_MS", "DEBUG") take their values from the
  * environment variables QSSM_<NAME> once, when the library is first used; afterwards only these two
  * calls change them, process-wide.  No launch reads the environment.  "TEST_SKIP_FIRST_CHUNK" (no
  * environment form) makes the single-pass kernels skip the first chunk of every chain, so that their

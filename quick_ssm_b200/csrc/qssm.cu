@@ -111,10 +111,10 @@ bool tma_ok(const void* ptr, long long B, long long L, long long D, long long sb
 // ---------------------------------------------------------------------------------------------
 enum Knob {
     K_GRID, K_V, K_TB, K_STAGES, K_NOUT, K_WIDE, K_FWD_TILE4, K_NO_TMA, K_L2HINT, K_CHAINED, K_CHUNK_ROWS,
-    K_CHAINED_GRID, K_CHAINED_HINT, K_WAIT_MS, K_DEBUG, K_TEST_SKIP_FIRST_CHUNK, K_COUNT
+    K_CHAINED_GRID, K_CHAINED_HINT, K_CHAINED_SLOTS, K_WAIT_MS, K_DEBUG, K_TEST_SKIP_FIRST_CHUNK, K_COUNT
 };
 const char* const kKnobNames[K_COUNT] = {"GRID", "V", "TB", "STAGES", "NOUT", "WIDE", "FWD_TILE4", "NO_TMA", "L2HINT",
-                                         "CHAINED", "CHUNK_ROWS", "CHAINED_GRID", "CHAINED_HINT", "WAIT_MS", "DEBUG",
+                                         "CHAINED", "CHUNK_ROWS", "CHAINED_GRID", "CHAINED_HINT", "CHAINED_SLOTS", "WAIT_MS", "DEBUG",
                                          "TEST_SKIP_FIRST_CHUNK"};
 constexpr int KNOB_UNSET = INT_MIN;
 
@@ -556,6 +556,12 @@ ChainedLayout chained_layout(long long B, long long L, long long D, int elem_siz
     long long need = (c.grid + c.n_chains - 1) / c.n_chains + 8;
     int slots = 4;
     while (slots < need) slots <<= 1;
+    // tests shrink the ring so that slots change hands while readers still look for the old owner
+    const int forced_slots = knob(K_CHAINED_SLOTS, 0);
+    if (forced_slots >= 2 && forced_slots < slots) {
+        slots = 2;
+        while (slots * 2 <= forced_slots) slots <<= 1;
+    }
     c.slots = slots;
     c.desc_off = 256;
     c.bytes = c.desc_off + (size_t)c.n_chains * slots * 96 * 16;

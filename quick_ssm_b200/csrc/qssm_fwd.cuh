@@ -411,6 +411,15 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
     bool ok = true;
     long long js = -1;      // nearest predecessor whose inclusive end state is known
     long long folded = 0;   // aggregates of chunks js+1 .. folded-1 are already applied to h
+    // A slot whose tag is LARGER than the one wanted has been taken over by a later chunk of the chain.
+    // That happens only after the old owner's successor has published its inclusive state
+    // (chained_slot_free), so a nearer inclusive state exists by now: start over from k - 1 with fresh
+    // loads instead of waiting for a tag that will never come back.  Every restart finds the chain further
+    // along; the count is bounded all the same.
+    int restarts = 0;
+restart:
+    js = -1;
+    folded = 0;
     for (long long top = k - 1; js < 0 && ok; top -= WIN) {
         float4 wi[WIN], wa[WIN], wh[WIN];
 #pragma unroll
@@ -423,10 +432,11 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                 wh[q] = __ldcg(dj + 32 + lane);
             }
         }
+        bool reused = false;
 #pragma unroll
         for (int q = 0; q < WIN; ++q) {
             const long long j = top - q;
-            if (j < 0 || js >= 0 || !ok) continue;
+            if (j < 0 || js >= 0 || !ok || reused) continue;
             const unsigned int want = (unsigned int)(j + 1);
             const float4* dj = cdesc + (size_t)(j & (slots - 1)) * 96;
             bool inc = __all_sync(0xffffffffu, __float_as_uint(wi[q].x) == want);
@@ -434,6 +444,11 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
             if (!inc && !agg) {  // nothing published yet: poll this chunk
                 const unsigned long long start = global_timer_ns();
                 for (unsigned int it = 0; ok; ++it) {
+                    if (__any_sync(0xffffffffu, __float_as_uint(wi[q].x) > want || __float_as_uint(wa[q].x) > want ||
+                                                    __float_as_uint(wh[q].x) > want)) {
+                        reused = true;
+                        break;
+                    }
                     wi[q] = __ldcg(dj + 64 + lane);
                     wa[q] = __ldcg(dj + lane);
                     wh[q] = __ldcg(dj + 32 + lane);
@@ -448,11 +463,15 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                     }
                 }
             }
-            if (ok && inc) {
+            if (ok && !reused && inc) {
                 h[0] = wi[q].y;
                 h[1] = wi[q].z;
                 js = j;
             }
+        }
+        if (reused) {
+            if (++restarts > 64) return false;
+            goto restart;
         }
         if (ok && js >= 0) {  // the aggregates of this window that lie after js are in registers: apply them now
             const int qf = (int)(top - js);
@@ -478,6 +497,19 @@ __device__ __forceinline__ bool chained_lookback(const float4* cdesc, int slots,
                 wa[q] = __ldcg(dj + lane);
                 wh[q] = __ldcg(dj + 32 + lane);
             }
+        }
+        // these chunks were seen published above, but a slot may have changed hands since: check the tags again
+        bool stale = false;
+#pragma unroll
+        for (int q = 0; q < WIN; ++q) {
+            if (base + q < k) {
+                const unsigned int want = (unsigned int)(base + q + 1);
+                stale = stale || __float_as_uint(wa[q].x) != want || __float_as_uint(wh[q].x) != want;
+            }
+        }
+        if (__any_sync(0xffffffffu, stale)) {
+            if (++restarts > 64) return false;
+            goto restart;
         }
 #pragma unroll
         for (int q = 0; q < WIN; ++q) {

@@ -336,6 +336,24 @@ def test_chained_single_pass_is_deterministic(tune):
             assert torch.equal(runs[0][k], other[k]), k
 
 
+@pytest.mark.parametrize("slots", [2, 4, 8])
+def test_chained_look_back_survives_descriptor_slots_changing_hands(tune, slots):
+    """A descriptor ring far smaller than the chunks of a chain in flight: chunks take over slots while
+    readers that loaded their window earlier still look for the old owner.  The look-back must notice (a
+    larger tag), start over and still deliver the same carries: results equal the oracle and are
+    bit-identical to a run with a roomy ring."""
+    tune("CHAINED", 2)
+    tune("CHUNK_ROWS", 32)
+    inp = make_inputs(1, 40000, 64, dtype=torch.float32, seed=37)   # one chain, 1250 chunks, hundreds of warps on it
+    ref = _oracle(inp, np.float64)
+    roomy = _run_scan(inp)
+    tune("CHAINED_SLOTS", slots)
+    tight = _run_scan(inp)
+    _check(tight, ref, torch.float32)
+    for k in roomy:
+        assert torch.equal(roomy[k], tight[k]), k
+
+
 @pytest.mark.parametrize("shape,dtype", [((2, 100, 72), torch.float32), ((3, 77, 200), torch.bfloat16),
                                          ((1, 50, 3), torch.float32), ((2, 300, 330), torch.float16)],
                          ids=["fp32", "bf16", "fp32_guarded_path", "fp16_wide"])
