@@ -1,9 +1,9 @@
 """Timing of the scan on the benchmark configurations other than the headline one.
 
-    python -m quick_ssm_b200.bench_configs --config cfg4 [--no-checkpoint]
+    python bench_configs.py --config cfg4 [--no-checkpoint]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m quick_ssm_b200.bench_configs --config cfg2 --shard seq      # time axis split over N GPUs
-        -m quick_ssm_b200.bench_configs --config cfg4 --shard batch    # batch split over N GPUs
+        bench_configs.py --config cfg2 --shard seq      # time axis split over N GPUs
+        bench_configs.py --config cfg4 --shard batch    # batch split over N GPUs
 
 Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
   cfg1       B=8  L=8192  D=4096 bf16                     (the headline; bench.py reports it)
@@ -23,13 +23,18 @@ import argparse
 import json
 import os
 import statistics
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 import torch
 import torch.distributed as dist
 
-from . import _lib
-from .sharded import CudaShardOps, shard_backward, shard_forward
-from .synth import CONFIGS, make_inputs
+from quick_ssm_b200 import _lib
+from quick_ssm_b200.sharded import CudaShardOps, shard_backward, shard_forward
+from quick_ssm_b200.synth import CONFIGS, make_inputs
 
 
 def _median_ms(fn, steps, warmup, sync):
@@ -50,7 +55,7 @@ def run_gates(args):
     """The scan of configuration 3 together with the layer's gate activations: fused kernels
     (`gated_scan`) against torch element-wise gates followed by `scan`, forward + backward through
     autograd, for fp32 projection outputs (fp32 parameters, the reference's setting) and bf16 ones."""
-    from .gated import _composed, gated_scan
+    from quick_ssm_b200.gated import _composed, gated_scan
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
@@ -83,7 +88,7 @@ def run_gates(args):
 def run_norm(args):
     """The pre-norm of configuration 3 (rows = 16 x 4096, hidden 1024): the normalisation kernels against
     torch's element-wise chain, forward + backward through autograd, fp32 and bf16 activations."""
-    from .norm import _composed, rms_norm
+    from quick_ssm_b200.norm import _composed, rms_norm
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
@@ -121,9 +126,9 @@ def run_norm(args):
 
 def run_stack(args):
     """Configuration 3: the scan inside a 12-layer SSM stack (projections stay torch GEMMs)."""
-    from . import scan_interface
-    from .gated import _GatedScanFunction
-    from .layers import SSM, SSMFused
+    from quick_ssm_b200 import scan_interface
+    from quick_ssm_b200.gated import _GatedScanFunction
+    from quick_ssm_b200.layers import SSM, SSMFused
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)

@@ -190,7 +190,11 @@ def forward_aggregate(ops, comm, xs, as_, bs) -> Exchange:
     """First half of a shard's forward: its aggregate, written into the send buffer of the exchange."""
     B, L, D = xs.shape
     ex = Exchange(comm, "f", B, D, xs.device)
-    if comm.rank == comm.world - 1:  # nobody comes after the last shard: identity aggregate, no read
+    # Nobody folds the last shard's aggregate, but that rank computes it all the same: the pass leaves the
+    # per-segment aggregates its own seeded scan reuses, and with identical work on every rank nobody waits
+    # at the exchange for a rank that started late.  (Skipping it was measured slower: the rank idles while
+    # the others aggregate and then scans without the segment aggregates.)  A lone rank has nobody to wait for.
+    if comm.world == 1:
         ex.set_identity()
     else:
         ops.aggregate_fwd(xs, as_, bs, ex.send[0], ex.send[1])
@@ -207,7 +211,7 @@ def forward_finish(ops, comm, ex: Exchange, xs, as_, bs, cs, y, tile_h, mark=lam
 def backward_aggregate(ops, comm, as_, cs, dy) -> Exchange:
     B, L, D = as_.shape
     ex = Exchange(comm, "b", B, D, as_.device)
-    if comm.rank == 0:  # nobody comes before the first shard
+    if comm.world == 1:  # see forward_aggregate: the first shard's aggregate is computed too
         ex.set_identity()
     else:
         ops.aggregate_bwd(as_, cs, dy, ex.send[0], ex.send[1])
