@@ -17,6 +17,9 @@ The same line carries, outside the headline value:
                  and h only (forward_only, 4 passes);
   api            the same step through the Python API, scan(...) + .backward() (autograd, allocations);
   host_call_us   host time of one qssm_scan_fwd + qssm_scan_bwd call pair on a tiny shape;
+  gpu_reference  optional third column: the reference's own Triton path (unmodified, installed under the
+                 git-ignored baseline/_ref) on the same GPU and inputs, a B=1 slice of the workload: its time, this
+                 library's time on the same slice, and the element-wise agreement of the two;
   seq_sharded    the long-sequence configuration (B=1, L=2^20, D=2048, fp16, decay close to one) with
                  the TIME axis split over the N ranks: per rank one aggregate pass, one NCCL all-gather
                  of 2*B*D floats, a fold and a seeded scan, forward and backward; at N=1 the single-pass
@@ -586,6 +589,16 @@ def run_gpu(args):
         host_call = measure_host_call(torch, _lib, dev)
     barrier()
 
+    # ---- optional third column: the reference's own Triton kernels on this GPU (rank 0, when installed) ----
+    gpu_reference = None
+    if rank == 0 and not args.no_ref_triton:
+        try:
+            import bench_configs
+            gpu_reference = bench_configs.ref_triton_compare(steps=3, warmup=1, L=L, local_rank=local)
+        except Exception as e:  # never let the optional column break the bench line
+            gpu_reference = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    barrier()
+
     # ---- the long-sequence configuration, time axis split over the ranks ----
     h2d_bytes, d2h_bytes = pipe.h2d_bytes, pipe.d2h_bytes
     del pipe, host, grads, y, tile_h, inp, x, a, b, c, dy
@@ -637,6 +650,7 @@ def run_gpu(args):
             "gpu_launches_e2e": e2e_launches * world,
             "clocks": clocks.summary(),
             "forward_only": fwd_only, "api": api, "host_call": host_call, "seq_sharded": seq,
+            "gpu_reference": gpu_reference,
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()
@@ -654,6 +668,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="profiling aid: device-resident loop only, no bench line")
     ap.add_argument("--no-seq", action="store_true", help="skip the sequence-sharded long-sequence leg")
+    ap.add_argument("--no-ref-triton", action="store_true", help="skip the reference's Triton kernels on this GPU")
     ap.add_argument("--seq-len", type=int, default=0, help="profiling aid: shorter L (same chains, less memory)")
     args = ap.parse_args()
     if args.impl == "reference":

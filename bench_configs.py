@@ -14,6 +14,9 @@ Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
              MSE loss to a random target: whole forward+backward step, with the time spent inside
              the scan kernels taken separately from CUDA events around every scan call
   cfg3_gates the same scan shape with the layer's gate activations: fused kernels vs torch gates + scan
+  cfg3_norm  the layer's pre-norm: the RMS-norm kernels vs torch's element-wise chain, and the kernels alone
+  ref_triton the reference's own Triton path (installed unmodified under the git-ignored baseline/_ref) on the
+             same GPU and inputs, a batch slice of cfg1: timing and element-wise agreement with this library
 With --shard the TOTAL problem is fixed and split over the ranks (strong scaling); the reported
 throughput is total elements over the slowest rank's device time.  One JSON line per run.
 """
@@ -124,6 +127,61 @@ def run_norm(args):
     print(json.dumps(out), flush=True)
 
 
+def run_ref_triton(args):
+    print(json.dumps(ref_triton_compare(args.steps, args.warmup, args.seq_len or 8192)), flush=True)
+
+
+def ref_triton_compare(steps: int, warmup: int, L: int = 8192, local_rank: int = 0) -> dict:
+    """The reference's own Triton path (`quick_ssm.scan_interface.scan`, backend "triton", installed unmodified
+    under baseline/_ref) on the same B200 and the same inputs as this library: a batch slice of configuration 1
+    (B=1, L=8192, D=4096, bf16; the reference needs about 7 GiB of fp32 scratch per batch entry pair, so the slice
+    keeps it small), forward + backward through autograd, plus the results of both compared element by element.
+    Optional third column next to the CPU baseline: a GPU-over-GPU ratio on identical hardware."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    out = {"config": "ref_triton"}
+    if not os.path.isdir(os.path.join(ref_dir, "quick_ssm")):
+        out["unavailable"] = "baseline/_ref/quick_ssm is not installed on this machine"
+        return out
+    sys.path.insert(0, ref_dir)
+    import importlib
+    ref_iface = importlib.import_module("quick_ssm.scan_interface")
+    from quick_ssm_b200 import scan as our_scan
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, D = 1, 4096
+    inp = make_inputs(B, L, D, dtype=torch.bfloat16, device=dev, seed=0)
+    out["shape"] = [B, L, D]
+    results = {}
+    for name, fn in (("ours", lambda *t: our_scan(*t, block_l=256, checkpoint=True)),
+                     ("reference_triton", lambda *t: ref_iface.scan(*t, block_l=256, checkpoint=True, backend="triton"))):
+        leaves = [t.detach().clone().requires_grad_() for t in inp.tensors()]
+
+        def step():
+            for t in leaves:
+                t.grad = None
+            y = fn(*leaves)
+            y.backward(inp.dy)
+            return y
+
+        y = step()   # first call: the reference compiles one kernel specialisation per shape here
+        torch.cuda.synchronize()
+        ms = _median_ms(step, steps, warmup, torch.cuda.synchronize)
+        results[name] = [y.detach()] + [t.grad.detach().clone() for t in leaves]
+        out[name] = {"fwd_bwd_ms": round(ms, 4), "gelems": B * L * D / (ms * 1e-3) / 1e9,
+                     "peak_mem_gib": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2)}
+        torch.cuda.reset_peak_memory_stats(dev)
+    out["speedup_over_reference_triton"] = out["reference_triton"]["fwd_bwd_ms"] / out["ours"]["fwd_bwd_ms"]
+    agree = {}
+    for k, u, v in zip(("y", "dx", "da", "db", "dc"), results["ours"], results["reference_triton"]):
+        d = (u.float() - v.float()).abs()
+        bad = d > 1e-3 * max(1.0, float(v.float().abs().max())) + 2e-2 * v.float().abs()
+        agree[k] = {"max_abs_diff": float(d.max()), "max_abs_ref": float(v.float().abs().max()), "outside": int(bad.sum())}
+    out["agreement_with_reference_triton"] = agree
+    out["all_within_tolerance"] = all(v["outside"] == 0 for v in agree.values())
+    return out
+
+
 def run_stack(args):
     """Configuration 3: the scan inside a 12-layer SSM stack (projections stay torch GEMMs)."""
     from quick_ssm_b200 import scan_interface
@@ -198,7 +256,7 @@ def run_stack(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm"])
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm", "ref_triton"])
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
@@ -213,6 +271,8 @@ def main():
         return run_gates(args)
     if args.config == "cfg3_norm":
         return run_norm(args)
+    if args.config == "ref_triton":
+        return run_ref_triton(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
