@@ -46,3 +46,30 @@ def test_forward_and_gradients_match_the_reference_triton_path(shape, block_l, d
     tol = dict(rtol=1e-3, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
     for name, u, v in zip(("y", "dx", "da", "db", "dc"), *res):
         assert torch.allclose(v.float(), u.float(), **tol), (name, float((v.float() - u.float()).abs().max()))
+
+
+def test_kernel_level_entry_points_match_the_reference_drivers():
+    """block_scan_forward_3d -> (cumulative prod a, h), block_scan_backward_3d -> four fp32 gradients and the
+    forward-only driver, reference (triton_forwards.py:134-172, triton_backwards.py:168-209,
+    forward_only.py:423-540) against the shims of this package with the same arguments."""
+    _reference_scan()
+    ref_f = importlib.import_module("quick_ssm.triton_forwards")
+    ref_b = importlib.import_module("quick_ssm.triton_backwards")
+    ref_o = importlib.import_module("quick_ssm.forward_only")
+    from quick_ssm_b200 import forward_only as our_o
+    from quick_ssm_b200 import triton_backwards as our_b
+    from quick_ssm_b200 import triton_forwards as our_f
+    inp = make_inputs(2, 1024, 8, dtype=torch.float32, seed=19).to("cuda")
+    x, a, b, c = inp.tensors()
+    ra, rh = ref_f.block_scan_forward_3d(x, a, b, 256)
+    oa, oh = our_f.block_scan_forward_3d(x, a, b, 256)
+    assert torch.allclose(oh, rh, rtol=1e-3, atol=1e-5)
+    assert torch.allclose(oa, ra, rtol=1e-3, atol=1e-30)   # cumulative products fall towards zero: relative only
+    rg = ref_b.block_scan_backward_3d(a, b, c, x, rh, inp.dy, 256)
+    og = our_b.block_scan_backward_3d(a, b, c, x, oh, inp.dy, 256)
+    for name, u, v in zip(("dx", "da", "db", "dc"), rg, og):
+        assert torch.allclose(v, u, rtol=1e-3, atol=2e-5), name
+    h_ref = ref_o.block_scan_forward_3d(x, a, b, 256)
+    h_our = our_o.block_scan_forward_3d(x, a, b, 256)
+    assert torch.allclose(h_our, h_ref, rtol=1e-3, atol=1e-5)
+    _lib.check_device_status(synchronize=True)
