@@ -329,6 +329,8 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
         if (t_end > g.L) t_end = g.L;
         const int n_tiles = (int)((t_end - t_begin + TB - 1) / TB);
         const int c0 = (int)d0, c2 = (int)b;
+        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
+        const float slot_word = chained_slot_peek(cdesc, cp.slots, kk, lane);
 
         int pf_item = 0;
         const int n_items = 2 * n_tiles;
@@ -395,7 +397,6 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
         if (!ok) break;
 
         // ---- carry: same descriptor protocol as the forward, in processing order kk ----
-        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
         float4* const mydesc = cdesc + (size_t)(kk & (cp.slots - 1)) * 96;
         const float mytag = __uint_as_float((unsigned int)(kk + 1));
         float G[V];
@@ -404,7 +405,7 @@ __global__ void __launch_bounds__(32) scan_bwd_chained_kernel(const __grid_const
             for (int i = 0; i < V; ++i)
                 G[i] = (p.g_in != nullptr && d_lane + i < g.D) ? p.g_in[b * g.D + d_lane + i] : 0.f;
         } else {
-            ok = chained_slot_free(cdesc, cp.slots, kk, lane, cp.wait_ns);
+            ok = chained_slot_free_peeked(slot_word, cdesc, cp.slots, kk, lane, cp.wait_ns);
             if (!ok) break;
             __stcg(mydesc + lane, make_float4(mytag, P[0], P[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, Q[0], Q[1], 0.f));

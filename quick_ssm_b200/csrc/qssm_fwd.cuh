@@ -389,6 +389,21 @@ __device__ __forceinline__ bool chained_slot_free(const float4* cdesc, int slots
     }
 }
 
+// The same check split in two so that its round trip to L2 overlaps the first pass of the chunk: the word is
+// asked for when the chunk starts and looked at when the aggregate is ready (it nearly always says "free").
+__device__ __forceinline__ float chained_slot_peek(const float4* cdesc, int slots, long long k, int lane) {
+    const long long j = k - slots + 1;
+    if (j < 0) return 0.f;
+    return __ldcg(cdesc + (size_t)(j & (slots - 1)) * 96 + 64 + lane).x;
+}
+__device__ __forceinline__ bool chained_slot_free_peeked(float peeked, const float4* cdesc, int slots, long long k,
+                                                         int lane, unsigned long long wait_ns) {
+    const long long j = k - slots + 1;
+    if (j < 0) return true;
+    if (__all_sync(0xffffffffu, __float_as_uint(peeked) == (unsigned int)(j + 1))) return true;
+    return chained_slot_free(cdesc, slots, k, lane, wait_ns);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Look-back over the chunk descriptors of one chain (chained kernels).
 //
@@ -590,6 +605,8 @@ __global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_const
         if (t_end > g.L) t_end = g.L;
         const int n_tiles = (int)((t_end - t_begin + TB - 1) / TB);
         const int c0 = (int)d0, c2 = (int)b;
+        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
+        const float slot_word = chained_slot_peek(cdesc, cp.slots, k, lane);
 
         // the tile stream of this chunk: n_tiles tiles of pass 1 (x, a, b), then n_tiles of pass 2 (x, a, b, c)
         int pf_item = 0;
@@ -642,7 +659,6 @@ __global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_const
         if (!ok) break;
 
         // ---- carry: publish aggregate, look back, publish inclusive end state ----
-        float4* const cdesc = reinterpret_cast<float4*>(cp.desc) + (size_t)c * cp.slots * 96;
         float4* const mydesc = cdesc + (size_t)(k & (cp.slots - 1)) * 96;
         const float mytag = __uint_as_float((unsigned int)(k + 1));
         float h[V];
@@ -651,7 +667,7 @@ __global__ void __launch_bounds__(32) scan_fwd_chained_kernel(const __grid_const
             for (int i = 0; i < V; ++i)
                 h[i] = (p.h_in != nullptr && d_lane + i < g.D) ? p.h_in[b * g.D + d_lane + i] : 0.f;
         } else {
-            ok = chained_slot_free(cdesc, cp.slots, k, lane, cp.wait_ns);
+            ok = chained_slot_free_peeked(slot_word, cdesc, cp.slots, k, lane, cp.wait_ns);
             if (!ok) break;
             __stcg(mydesc + lane, make_float4(mytag, A[0], A[1], 0.f));
             __stcg(mydesc + 32 + lane, make_float4(mytag, H[0], H[1], 0.f));

@@ -112,3 +112,58 @@ def test_fold_reads_the_gathered_buffer_in_place():
             for k in ks:
                 run = A[k].double().cpu().numpy() * run + H[k].double().cpu().numpy()
             assert np.allclose(got.cpu().numpy(), run, rtol=1e-5, atol=1e-6)
+
+
+def test_full_size_long_sequence_in_eight_shards():
+    """The long-sequence benchmark configuration (B=1, L=2^20, D=2048, fp16, decay close to one) at full size,
+    cut into eight shards run one after the other on this GPU: the sharded result must agree with the unsharded
+    one everywhere (same kernels' arithmetic, different carries' rounding) and with the oracle on whole strips."""
+    from quick_ssm_b200.synth import make_config
+    inp = make_config("cfg2", device=DEV)
+    x, a, b, c = inp.tensors()
+    dy = inp.dy
+    B, L, D = x.shape
+    G = 8
+    bounds = _bounds(L, G, False)
+    shards = [[t[:, lo:hi] for t in (x, a, b, c, dy)] for lo, hi in bounds]
+    comms = [BoardComm(r, G) for r in range(G)]
+    ops = [sharded.CudaShardOps() for _ in range(G)]
+    y = torch.empty_like(x)
+    tile_h = torch.empty((B, L // 16, D), dtype=torch.float32, device=DEV)
+    grads = [torch.empty_like(x) for _ in range(4)]
+    exs = [sharded.forward_aggregate(ops[r], comms[r], *shards[r][:3]) for r in range(G)]
+    board = torch.stack([ex.send for ex in exs])
+    for r, (lo, hi) in enumerate(bounds):
+        comms[r].board = board
+        sharded.forward_finish(ops[r], comms[r], exs[r], *shards[r][:4], y[:, lo:hi], tile_h[:, lo // 16:hi // 16])
+    exs = [sharded.backward_aggregate(ops[r], comms[r], shards[r][1], shards[r][3], shards[r][4]) for r in range(G)]
+    board = torch.stack([ex.send for ex in exs])
+    for r, (lo, hi) in enumerate(bounds):
+        comms[r].board = board
+        sharded.backward_finish(ops[r], comms[r], exs[r], *shards[r], tile_h[:, lo // 16:hi // 16],
+                                [g[:, lo:hi] for g in grads])
+    _lib.check_device_status(synchronize=True)
+
+    # oracle on three 64-channel strips over all 2^20 steps
+    for d0 in (0, 1024, D - 64):
+        sl = (slice(None), slice(None), slice(d0, d0 + 64))
+        f = [t[sl].float().cpu() for t in (x, a, b, c, dy)]
+        _, y_ref, _ = so.scan_forward(*f[:4], dtype=np.float32)
+        g_ref = so.scan_backward(*f, dtype=np.float32)[:4]
+        assert_close_half(y[sl], y_ref, f"y[{d0}]")
+        for name, g, r in zip(("dx", "da", "db", "dc"), grads, g_ref):
+            assert_close_half(g[sl], r, f"{name}[{d0}]", scale_atol=max(1.0, float(np.abs(r).max())))
+
+    # the unsharded scan (single-pass kernels) on the same tensors: element-wise agreement over everything
+    y1 = torch.empty_like(x)
+    g1 = [torch.empty_like(x) for _ in range(4)]
+    _lib.scan_fwd(x, a, b, c, y1, tile_h=tile_h)
+    _lib.scan_bwd(x, a, b, c, dy, *g1, tile_h=tile_h)
+    _lib.check_device_status(synchronize=True)
+    chunk = 1 << 27
+    for got, ref, name in zip([y] + grads, [y1] + g1, ("y", "dx", "da", "db", "dc")):
+        scale = max(1.0, float(ref.float().abs().max()))
+        fg, fr = got.reshape(-1), ref.reshape(-1)
+        for lo in range(0, fg.numel(), chunk):
+            u, v = fg[lo:lo + chunk].float(), fr[lo:lo + chunk].float()
+            assert bool(((u - v).abs() <= 1e-3 * scale + 2e-2 * v.abs()).all()), name
