@@ -15,6 +15,8 @@ Configurations (seeded synthetic inputs, see ``synth.CONFIGS``):
              the scan kernels taken separately from CUDA events around every scan call
   cfg3_gates the same scan shape with the layer's gate activations: fused kernels vs torch gates + scan
   cfg3_norm  the layer's pre-norm: the RMS-norm kernels vs torch's element-wise chain, and the kernels alone
+  strips     launch-shape sweep: D=2048, 2^27 elements, B = 1..32 (32..1024 strips of 64 channels), --dtype fp32|bf16|fp16;
+             one JSON line per batch size with forward / backward ms and the fraction of the copy peak
   ref_triton the reference's own Triton path (installed unmodified under the git-ignored baseline/_ref) on the
              same GPU and inputs, a batch slice of cfg1: timing and element-wise agreement with this library
 With --shard the TOTAL problem is fixed and split over the ranks (strong scaling); the reported
@@ -125,6 +127,42 @@ def run_norm(args):
                      "kernel_fwd_ms": round(k_fwd, 4), "kernel_fwd_gbs_of_2s_bytes": n * 2 * s / (k_fwd * 1e-3) / 1e9,
                      "kernel_bwd_ms": round(k_bwd, 4), "kernel_bwd_gbs_of_3s_bytes": n * 3 * s / (k_bwd * 1e-3) / 1e9}
     print(json.dumps(out), flush=True)
+
+
+def run_strips(args):
+    """Forward + backward on a fixed element count while the number of 64-channel strips (batch x D/64) goes from
+    far fewer than the SMs to several per SM: shows which launch shape the library picks for each count."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]
+    D = 2048
+    peak = _copy_peak_gbs()
+    for B in (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 32):
+        L = ((1 << 27) // (B * D)) // 256 * 256
+        inp = make_inputs(B, L, D, dtype=dtype, device=dev, seed=0)
+        x, a, b, c = inp.tensors()
+        y = torch.empty_like(x)
+        tile_h = torch.empty((B, L // _lib.tile_rows(), D), dtype=torch.float32, device=dev)
+        grads = [torch.empty_like(x) for _ in range(4)]
+        f = _median_ms(lambda: _lib.scan_fwd(x, a, b, c, y, tile_h=tile_h), args.steps, args.warmup, torch.cuda.synchronize)
+        g = _median_ms(lambda: _lib.scan_bwd(x, a, b, c, inp.dy, *grads, tile_h=tile_h), args.steps, args.warmup,
+                       torch.cuda.synchronize)
+        _lib.check_device_status(synchronize=True)
+        n, s = B * L * D, x.element_size()
+        print(json.dumps({"config": "strips", "dtype": args.dtype, "B": B, "L": L, "D": D, "strips": B * D // 64,
+                          "fwd_ms": round(f, 4), "bwd_ms": round(g, 4),
+                          "fwd_gbs": round(n * 5 * s / f / 1e6, 1), "bwd_gbs": round(n * 9 * s / g / 1e6, 1),
+                          "frac_of_copy_peak": round(n * 14 * s / (f + g) / 1e6 / peak, 3)}), flush=True)
+        del inp, x, a, b, c, y, tile_h, grads
+        torch.cuda.empty_cache()
+
+
+def _copy_peak_gbs() -> float:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return 6650.0  # an earlier measurement on the same pool
 
 
 def run_ref_triton(args):
@@ -256,7 +294,8 @@ def run_stack(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm", "ref_triton"])
+    ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm", "strips", "ref_triton"])
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16", "fp16"], help="strips: storage type")
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
@@ -271,6 +310,8 @@ def main():
         return run_gates(args)
     if args.config == "cfg3_norm":
         return run_norm(args)
+    if args.config == "strips":
+        return run_strips(args)
     if args.config == "ref_triton":
         return run_ref_triton(args)
 

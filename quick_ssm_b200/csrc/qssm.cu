@@ -278,11 +278,15 @@ long long concurrent_chains_gated(long long chains) {
 // per element, so one warp moves twice the bytes; narrow strips (V = 1) are for channel counts
 // that would leave half of a wide strip empty, or for launches with too few chains to give
 // every SM two warps even after the time axis has been segmented.
-int pick_v(long long B, long long D, int n_seg) {
+int pick_v(long long B, long long D, int n_seg, int elem_size = 0) {
     const int forced = knob(K_V, 0);
     if (forced == 1 || forced == 2) return forced;
     if (D <= 32) return 1;
     const long long chains_v2 = B * ((D + 63) / 64) * (n_seg < 1 ? 1 : n_seg);
+    // fp32 rows are twice as long, so a warp has twice the bytes in flight and wide strips pay from 1.2 chains
+    // per SM on (192 wide chains on 148 SMs: 0.93 of the copy peak forward + backward against 0.89 narrow;
+    // 160: 0.82 wide against 0.95 narrow)
+    if (elem_size == 4 && n_seg <= 1) return 5 * chains_v2 >= 6ll * sm_count() ? 2 : 1;
     return chains_v2 >= 2ll * sm_count() ? 2 : 1;
 }
 int pick_tb() {
@@ -295,6 +299,24 @@ int pick_tb() {
 // every backward lose (4.5 against 6.5 TB/s, 4.8 against 6.25), so they stay on 16 rows.
 bool prefers_tall_tiles(int in_dtype, int V) { return knob(K_TB, 0) == 0 && dtype_size(in_dtype) == 2 && V == 2; }
 
+// fp32 storage, one pass over an unsegmented time axis, h rebuilt from the tile states.  Tiles of 32 rows double
+// the bytes a warp keeps in flight, which is what a launch with few chains lacks; with many chains they help the
+// backward only (two 40 KB stages, two CTAs per SM).  Measured on B200 (148 SMs), D = 2048, 2^27 elements,
+// forward / backward in GB/s of the 5 / 9 tensor passes, 16 against 32 rows:
+//   narrow strips  128 wide-strip equivalents: 4029/5226 -> 5716/5666    160: 5006/5632 -> 6713/6012
+//   wide strips    192: 5566/5500 -> 6274/6002    256: 6846/6216 -> 6783/5654    320: 6792/6084 -> 4821/4778
+//                  512: 6846/5737 -> 6742/6103   1024: 6840/5731 -> 6748/6035
+int f32_tile_rows(int V, long long chains, bool backward) {
+    const long long sms = sm_count();
+    if (V == 1) return 2 * chains < 5 * sms ? 32 : 16;
+    if (2 * chains < 3 * sms) return 32;
+    return backward && chains >= 3 * sms ? 32 : 16;
+}
+
+// fp32 storage keeps a GPU busy with one warp per chain from three quarters of a wide chain per SM on: one pass
+// with 128 wide-strip equivalents runs at 0.87 of the copy peak (forward + backward), 160 at 0.95, 256 at 0.98,
+// where the single-pass chained kernels stay at 0.73 whatever the chain count and segmenting the time axis at 0.68.
+bool f32_one_pass(long long chains_v2, int elem_size) { return elem_size == 4 && 4 * chains_v2 >= 3ll * sm_count(); }
 
 // Segment count.  Cutting the time axis costs an extra read of the tensors the carry depends on
 // (8 instead of 5 tensor passes forward, 12 instead of 9 backward), so it pays only when batch x
@@ -303,7 +325,7 @@ int auto_segments(long long B, long long L, long long D, int in_dtype) {
     if (B <= 0 || L <= 0 || D <= 0 || dtype_size(in_dtype) == 0) return 1;
     const long long chains = B * ((D + 63) / 64);
     const long long sms = sm_count();
-    if (chains >= 2 * sms) return 1;
+    if (chains >= 2 * sms || f32_one_pass(chains, dtype_size(in_dtype))) return 1;
     long long want = (4 * sms) / chains;  // rounded down: never more chains than four per SM hold at once
     const long long max_by_len = L / 256;  // at least 256 rows per segment
     if (want > max_by_len) want = max_by_len;
@@ -347,12 +369,13 @@ int pick_stages(long long grid, int stage_bytes, int store_bytes, int fixed_byte
     return best;
 }
 
-int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* status, int force_v = 0) {
+int make_plan(Plan& pl, long long B, long long L, long long D, int n_seg, int* status, int force_v = 0,
+              int elem_size = 0) {
     if (n_seg < 1) n_seg = 1;
     long long seg_rows = (L + n_seg - 1) / n_seg;
     seg_rows = ((seg_rows + 31) / 32) * 32;  // whole tiles for either tile height
     n_seg = (int)((L + seg_rows - 1) / seg_rows);
-    pl.V = pick_v(B, D, n_seg);
+    pl.V = pick_v(B, D, n_seg, elem_size);
     if (force_v > 0 && knob(K_V, 0) == 0) pl.V = force_v;
     pl.TB = pick_tb();
     const int chans = 32 * pl.V;
@@ -584,6 +607,7 @@ size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
     // measured crossover: below about 2.75 chains per SM the chained kernels (~182 Gelem/s fwd+bwd on
     // 16-bit data whatever the chain count) beat one warp per chain (168 at 384 chains, 196 at 448)
     if (mode == 1 && 4 * B * ((D + 63) / 64) >= 11 * (long long)sm_count()) return 0;
+    if (mode == 1 && f32_one_pass(B * ((D + 63) / 64), dtype_size(in_dtype))) return 0;
     const size_t f = chained_layout(B, L, D, dtype_size(in_dtype), false).bytes;
     const size_t r = chained_layout(B, L, D, dtype_size(in_dtype), true).bytes;
     return f > r ? f : r;
@@ -765,7 +789,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, n_seg, status_word))) return rc;
+    if ((rc = make_plan(pl, B, L, D, n_seg, status_word, 0, dtype_size(in_dtype)))) return rc;
     n_seg = pl.g.n_seg;
 
     const float* seeds = h_in;
@@ -788,6 +812,8 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
     fp.g = pl.g;
     const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
     if (prefers_tall_tiles(in_dtype, pl.V) && eo == 2 && h_saved == nullptr && knob(K_FWD_TILE4, 0) == 0) pl.TB = 32;
+    if (es == 4 && pl.g.n_seg == 1 && h_saved == nullptr && knob(K_TB, 0) == 0)
+        pl.TB = f32_tile_rows(pl.V, pl.chains, false);
     const int chans = 32 * pl.V, TB = pl.TB;
     const long long hs_sb = L * D, hs_sl = D;
     bool tma = knob(K_NO_TMA, 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
@@ -988,7 +1014,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     int n_seg = 1;
     if ((rc = resolve_segments(n_seg_req, B, L, D, in_dtype, ws, ws_bytes, &n_seg))) return rc;
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, n_seg, status_word))) return rc;
+    if ((rc = make_plan(pl, B, L, D, n_seg, status_word, 0, dtype_size(in_dtype)))) return rc;
     n_seg = pl.g.n_seg;
 
     const float* seeds = g_in;
@@ -1010,8 +1036,9 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
     memset(&bp, 0, sizeof(bp));
     bp.g = pl.g;
     const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
-    const int chans = 32 * pl.V, TB = pl.TB;
     const bool saved = h_saved != nullptr;
+    if (es == 4 && pl.g.n_seg == 1 && !saved && knob(K_TB, 0) == 0) pl.TB = f32_tile_rows(pl.V, pl.chains, true);
+    const int chans = 32 * pl.V, TB = pl.TB;
     const long long n_tiles_b = (L + TS - 1) / TS;
     const long long g_sb = L * D, g_sl = D;  // gradients and h_saved are contiguous
     bool tma = knob(K_NO_TMA, 0) == 0 && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&

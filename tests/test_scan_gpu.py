@@ -402,6 +402,23 @@ def test_every_kernel_variant_gives_the_same_answer(tune, env):
             assert torch.allclose(got[k].float(), base[k].float(), rtol=2e-2, atol=1e-3), k
 
 
+@pytest.mark.parametrize("shape", [(4, 203, 2048), (3, 203, 4070), (4, 203, 4096), (8, 150, 4096)],
+                         ids=["128_strips_narrow_tall", "192_strips_wide_tall", "256_strips_wide", "512_strips_tall_backward"])
+@pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
+def test_fp32_mid_chain_counts_run_one_pass_and_match_float64(shape, checkpoint):
+    """fp32 storage with between about one and four wide strips per SM: the library runs these as one pass with
+    one warp per strip (no time segments, no chained kernels) and picks strip width and tile height by the strip
+    count; each of the four choices is checked against the float64 loop, with a ragged last tile in time."""
+    B, L, D = shape
+    if torch.cuda.get_device_properties(0).multi_processor_count == 148:
+        assert _lib.auto_segments(B, L, D, torch.float32) == 1
+        assert _lib.load().qssm_workspace_bytes(B, 1 << 16, D, _lib.dtype_code(torch.float32)) == 0
+    inp = make_inputs(B, L, D, dtype=torch.float32, seed=59)
+    ref = _oracle(inp, np.float64)
+    got = _run_scan(inp, checkpoint=checkpoint)
+    _check(got, ref, torch.float32)
+
+
 @pytest.mark.parametrize("shape,dtype,out_dtype", [((8, 200, 4096), torch.bfloat16, None),
                                                    ((8, 200, 4000), torch.float16, None),
                                                    ((9, 137, 3784), torch.bfloat16, torch.float32)],
