@@ -313,10 +313,10 @@ int f32_tile_rows(int V, long long chains, bool backward) {
     return backward && chains >= 3 * sms ? 32 : 16;
 }
 
-// fp32 storage keeps a GPU busy with one warp per chain from three quarters of a wide chain per SM on: one pass
-// with 128 wide-strip equivalents runs at 0.87 of the copy peak (forward + backward), 160 at 0.95, 256 at 0.98,
-// where the single-pass chained kernels stay at 0.73 whatever the chain count and segmenting the time axis at 0.68.
-bool f32_one_pass(long long chains_v2, int elem_size) { return elem_size == 4 && 4 * chains_v2 >= 3ll * sm_count(); }
+// fp32 storage: the forward runs at the copy rate with one warp per strip from one wide strip per SM on (160 strips
+// on 148 SMs: 6.70 TB/s, the chained forward 5.82 at any count), below that the chained forward wins (128: 5.84
+// against 5.71, 96: 5.85 against 4.30); segmenting the time axis never does (0.68 of the copy peak).
+bool f32_one_pass(long long chains_v2, int elem_size) { return elem_size == 4 && chains_v2 >= (long long)sm_count(); }
 
 // Segment count.  Cutting the time axis costs an extra read of the tensors the carry depends on
 // (8 instead of 5 tensor passes forward, 12 instead of 9 backward), so it pays only when batch x
@@ -565,17 +565,21 @@ int chained_mode() { return knob(K_CHAINED, 1); }
 // traffic; shorter chunks mean more look-backs.  Measured on B200, 1 x 2^20 x 2048 fp16: the forward is
 // fastest with 192-224 rows (3.67 ms; 256: 3.81, 160: 3.77, 128: 3.84), the backward with 128 rows and
 // two stages, which lets nine CTAs share an SM (6.83 ms; 256 rows and four stages: 6.93); 512 rows
-// overflow the L2 and the second pass reads HBM again.
+// overflow the L2 and the second pass reads HBM again.  fp32 rows are twice as long: two stages (five CTAs
+// per SM instead of three forward, two backward) and chunks of 112 / 64 rows took 1 x 65536 x 2048 fp32 from
+// 4.71 / 4.82 TB/s forward / backward (128 rows, three / four stages) to 5.87 / 6.44; forward 96: 5.85,
+// 128: 5.84, 160: 5.63, 256: 4.66; backward 48: 6.33, 80: 6.36, 96: 6.26; eight CTAs' worth of grid, which
+// residency cuts to five, loses 1-5 % in the backward to uneven last rounds.
 ChainedLayout chained_layout(long long B, long long L, long long D, int elem_size, bool backward) {
     ChainedLayout c;
     c.n_chains = B * ((D + 63) / 64);
-    c.chunk_rows = knob(K_CHUNK_ROWS, elem_size == 2 ? (backward ? 128 : 192) : 128);
+    c.chunk_rows = knob(K_CHUNK_ROWS, elem_size == 2 ? (backward ? 128 : 192) : (backward ? 64 : 112));
     if (c.chunk_rows < TS) c.chunk_rows = TS;
     c.chunk_rows = (c.chunk_rows / TS) * TS;
     c.n_chunks = (int)((L + c.chunk_rows - 1) / c.chunk_rows);
     // two warps per scheduler: the two passes make a lone warp per scheduler compute-bound
     c.grid = knob(K_CHAINED_GRID, 0) > 0 ? knob(K_CHAINED_GRID, 0)
-                                                  : (backward && elem_size == 2 ? 9ll : 8ll) * sm_count();
+                                                  : (elem_size == 2 ? (backward ? 9ll : 8ll) : 5ll) * sm_count();
     const long long total = c.n_chains * c.n_chunks;
     if (c.grid > total) c.grid = total;
     if (c.grid < 1) c.grid = 1;
@@ -601,15 +605,28 @@ bool chained_shape_ok(long long B, long long L, long long D) {
     return B > 0 && L >= 4 * TS && D > 32 && B * ((D + 63) / 64) * ((L + TS - 1) / TS) < 0x7fffffffll;
 }
 
-size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype) {
+// Which launches take the chained kernels by themselves (mode 1).  16-bit storage: below about 2.75 strips
+// per SM the chained kernels (~182 Gelem/s fwd+bwd whatever the strip count) beat one warp per strip (168 at
+// 384 strips, 196 at 448).  fp32 storage: the forward below one strip per SM (f32_one_pass); the backward up to
+// five strips per SM, where it holds 6.1-6.4 TB/s at every strip count while one warp per strip swings between
+// 5.6 and 6.5 with how evenly the strips fill the SMs (416: 6.13 against 5.70, 640: 6.14 against 5.70,
+// 288: 6.24 against 6.50; level from 768 strips on).
+bool chained_wanted(long long B, long long L, long long D, int in_dtype, bool backward) {
     const int mode = chained_mode();
-    if (mode == 0 || !chained_shape_ok(B, L, D)) return 0;
-    // measured crossover: below about 2.75 chains per SM the chained kernels (~182 Gelem/s fwd+bwd on
-    // 16-bit data whatever the chain count) beat one warp per chain (168 at 384 chains, 196 at 448)
-    if (mode == 1 && 4 * B * ((D + 63) / 64) >= 11 * (long long)sm_count()) return 0;
-    if (mode == 1 && f32_one_pass(B * ((D + 63) / 64), dtype_size(in_dtype))) return 0;
-    const size_t f = chained_layout(B, L, D, dtype_size(in_dtype), false).bytes;
-    const size_t r = chained_layout(B, L, D, dtype_size(in_dtype), true).bytes;
+    if (mode == 0 || !chained_shape_ok(B, L, D)) return false;
+    if (mode != 1) return true;
+    const long long strips = B * ((D + 63) / 64), sms = sm_count();
+    if (dtype_size(in_dtype) == 4) return backward ? strips < 5 * sms : !f32_one_pass(strips, 4);
+    return 4 * strips < 11 * sms;
+}
+
+// Workspace of the chained kernels for one direction, 0 when that direction does not take them.
+size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype, bool backward) {
+    if (!chained_wanted(B, L, D, in_dtype, backward)) return 0;
+    return chained_layout(B, L, D, dtype_size(in_dtype), backward).bytes;
+}
+size_t chained_ws_bytes_any(long long B, long long L, long long D, int in_dtype) {
+    const size_t f = chained_ws_bytes(B, L, D, in_dtype, false), r = chained_ws_bytes(B, L, D, in_dtype, true);
     return f > r ? f : r;
 }
 
@@ -702,7 +719,7 @@ const char* qssm_status_string(int code) {
 
 size_t qssm_workspace_bytes(int64_t B, int64_t L, int64_t D, int in_dtype) {
     const size_t seg = ws_bytes_for(B, D, auto_segments(B, L, D, in_dtype));
-    const size_t chained = chained_ws_bytes(B, L, D, in_dtype);
+    const size_t chained = chained_ws_bytes_any(B, L, D, in_dtype);
     return seg > chained ? seg : chained;
 }
 
@@ -730,7 +747,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
 
     // Few chains, long sequence: single-pass chained kernel instead of aggregate + carry + scan.
     if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
-        const size_t need = chained_ws_bytes(B, L, D, in_dtype);
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype, false);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
             tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
@@ -747,8 +764,8 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
             g.l2_hint = knob(K_CHAINED_HINT, 1);
             g.status = status_word;
             g.n_chains = lay.n_chains;
-            g.n_out = 3;
-            g.n_stages = knob(K_STAGES, 0) >= 2 && knob(K_STAGES, 0) <= 8 ? knob(K_STAGES, 0) : 3;
+            g.n_out = knob(K_NOUT, 0) == 2 ? 2 : 3;
+            g.n_stages = knob(K_STAGES, 0) >= 2 && knob(K_STAGES, 0) <= 8 ? knob(K_STAGES, 0) : (es == 2 ? 3 : 2);
             const int chans = 64;
             if ((rc = fill_desc(cp.f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
             if ((rc = fill_desc(cp.f.a, a, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;
@@ -913,7 +930,7 @@ int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const v
     const int n_seg = n_seg_req != 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
     size_t need = ws_bytes_for(B, D, n_seg);
     if (n_seg_req == 0 && h_saved == nullptr) {
-        const size_t chained = chained_ws_bytes(B, L, D, in_dtype);
+        const size_t chained = chained_ws_bytes(B, L, D, in_dtype, false);
         if (chained > need) need = chained;
     }
     if (need > (size_t)QSSM_STATIC_WS_BYTES) return QSSM_E_STATIC_WS;
@@ -950,7 +967,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
 
     // Few chains, long sequence: single-pass chained kernel (h rebuilt from tile_h only).
     if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
-        const size_t need = chained_ws_bytes(B, L, D, in_dtype);
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype, true);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         const long long n_tiles_b = (L + TS - 1) / TS;
         const long long g_sb = L * D, g_sl = D;
@@ -972,7 +989,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
             g.status = status_word;
             g.n_chains = lay.n_chains;
             g.n_stages = knob(K_STAGES, 0) >= 2 && knob(K_STAGES, 0) <= 8 ? knob(K_STAGES, 0)
-                                                                                          : (es == 2 ? 2 : 4);
+                                                                                          : 2;
             const int chans = 64;
             BwdParams& f = cp.f;
             if ((rc = fill_desc(f.x, x, in_dtype, B, L, D, in_stride_b, in_stride_l, chans, TS, true))) return rc;

@@ -402,20 +402,32 @@ def test_every_kernel_variant_gives_the_same_answer(tune, env):
             assert torch.allclose(got[k].float(), base[k].float(), rtol=2e-2, atol=1e-3), k
 
 
-@pytest.mark.parametrize("shape", [(4, 203, 2048), (3, 203, 4070), (4, 203, 4096), (8, 150, 4096)],
-                         ids=["128_strips_narrow_tall", "192_strips_wide_tall", "256_strips_wide", "512_strips_tall_backward"])
-@pytest.mark.parametrize("checkpoint", [True, False], ids=["ckpt", "saved_h"])
-def test_fp32_mid_chain_counts_run_one_pass_and_match_float64(shape, checkpoint):
-    """fp32 storage with between about one and four wide strips per SM: the library runs these as one pass with
-    one warp per strip (no time segments, no chained kernels) and picks strip width and tile height by the strip
-    count; each of the four choices is checked against the float64 loop, with a ragged last tile in time."""
+@pytest.mark.parametrize("shape", [(1, 9000, 2048), (4, 203, 2048), (5, 203, 2048), (3, 203, 4070), (4, 203, 4096),
+                                   (12, 150, 4096)],
+                         ids=["32_strips_long", "128_strips", "160_strips", "192_strips", "256_strips", "768_strips"])
+@pytest.mark.parametrize("route", ["auto", "one_pass"])
+def test_fp32_launch_shapes_by_strip_count_match_float64(shape, route):
+    """fp32 storage picks its launch shape by the number of 64-channel strips: below one strip per SM both
+    directions take the chained kernels, above it the forward runs one warp per strip (narrow or wide strips,
+    16- or 32-row tiles) while the backward stays chained up to five strips per SM and then takes 32-row tiles.
+    `one_pass` forces one warp per strip in both directions (n_seg = 1), which reaches the tile-height choices
+    the automatic route leaves to the chained kernels.  Ragged last tile in time, ragged last strip."""
     B, L, D = shape
-    if torch.cuda.get_device_properties(0).multi_processor_count == 148:
-        assert _lib.auto_segments(B, L, D, torch.float32) == 1
-        assert _lib.load().qssm_workspace_bytes(B, 1 << 16, D, _lib.dtype_code(torch.float32)) == 0
     inp = make_inputs(B, L, D, dtype=torch.float32, seed=59)
     ref = _oracle(inp, np.float64)
-    got = _run_scan(inp, checkpoint=checkpoint)
+    if route == "auto":
+        if torch.cuda.get_device_properties(0).multi_processor_count == 148 and B * ((D + 63) // 64) >= 148:
+            assert _lib.auto_segments(B, 1 << 16, D, torch.float32) == 1
+        got = _run_scan(inp)
+    else:
+        x, a, b, c, dy = (t.to(DEV) for t in (inp.x, inp.a, inp.b, inp.c, inp.dy))
+        y = torch.empty_like(x)
+        th = torch.empty((B, (L + 15) // 16, D), dtype=torch.float32, device=DEV)
+        g = [torch.empty_like(x) for _ in range(4)]
+        _lib.scan_fwd(x, a, b, c, y, tile_h=th, n_seg=1)
+        _lib.scan_bwd(x, a, b, c, dy, *g, tile_h=th, n_seg=1)
+        _lib.check_device_status(synchronize=True)
+        got = dict(y=y, dx=g[0], da=g[1], db=g[2], dc=g[3])
     _check(got, ref, torch.float32)
 
 
