@@ -84,9 +84,11 @@ int qssm_tile_rows(void);
 /*
  * Bytes of scratch (`ws`) that lets qssm_scan_fwd / qssm_scan_bwd /
  * qssm_scan_aggregate_* split the time axis into parallel segments when B*D
- * alone gives the GPU too few independent recurrences.  0 means no scratch is
+ * alone gives the GPU too few independent recurrences, or run such a shape with
+ * the single-pass chained kernels (ticket counter and chunk descriptors; the
+ * larger of the forward's and the backward's need).  0 means no scratch is
  * ever used for this shape.  Passing less (or NULL) is legal: the call then
- * runs unsegmented.
+ * runs unsegmented with one warp per strip.
  * Replaces the scratch the reference allocates on every call
  * (triton_forwards.py:152-162, triton_backwards.py:188-199).
  */
