@@ -607,26 +607,32 @@ bool chained_shape_ok(long long B, long long L, long long D) {
 
 // Which launches take the chained kernels by themselves (mode 1).  16-bit storage: below about 2.75 strips
 // per SM the chained kernels (~182 Gelem/s fwd+bwd whatever the strip count) beat one warp per strip (168 at
-// 384 strips, 196 at 448).  fp32 storage: the forward below one strip per SM (f32_one_pass); the backward up to
+// 384 strips, 196 at 448); the forward with 16-bit output leaves them at two strips per SM already, where wide
+// strips on 32-row tiles overtake them (2^28 elements, D = 2048, bf16, TB/s: 320 strips 5.67 against 5.32 chained,
+// 352: 6.15 against 5.37, 384: 6.53 against 5.28; 288: 5.12 against 5.37; the backward gains at most 4 %).
+// fp32 storage: the forward below one strip per SM (f32_one_pass); the backward up to
 // five strips per SM, where it holds 6.1-6.4 TB/s at every strip count while one warp per strip swings between
 // 5.6 and 6.5 with how evenly the strips fill the SMs (416: 6.13 against 5.70, 640: 6.14 against 5.70,
 // 288: 6.24 against 6.50; level from 768 strips on).
-bool chained_wanted(long long B, long long L, long long D, int in_dtype, bool backward) {
+bool chained_wanted(long long B, long long L, long long D, int in_dtype, int out_dtype, bool backward) {
     const int mode = chained_mode();
     if (mode == 0 || !chained_shape_ok(B, L, D)) return false;
     if (mode != 1) return true;
     const long long strips = B * ((D + 63) / 64), sms = sm_count();
     if (dtype_size(in_dtype) == 4) return backward ? strips < 5 * sms : !f32_one_pass(strips, 4);
+    if (!backward && dtype_size(out_dtype) == 2 && knob(K_TB, 0) == 0) return strips < 2 * sms;
     return 4 * strips < 11 * sms;
 }
 
 // Workspace of the chained kernels for one direction, 0 when that direction does not take them.
-size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype, bool backward) {
-    if (!chained_wanted(B, L, D, in_dtype, backward)) return 0;
+size_t chained_ws_bytes(long long B, long long L, long long D, int in_dtype, int out_dtype, bool backward) {
+    if (!chained_wanted(B, L, D, in_dtype, out_dtype, backward)) return 0;
     return chained_layout(B, L, D, dtype_size(in_dtype), backward).bytes;
 }
+// Either direction, whatever the type of y / dy.
 size_t chained_ws_bytes_any(long long B, long long L, long long D, int in_dtype) {
-    const size_t f = chained_ws_bytes(B, L, D, in_dtype, false), r = chained_ws_bytes(B, L, D, in_dtype, true);
+    const size_t f = chained_ws_bytes(B, L, D, in_dtype, QSSM_F32, false);
+    const size_t r = chained_ws_bytes(B, L, D, in_dtype, QSSM_F32, true);
     return f > r ? f : r;
 }
 
@@ -747,7 +753,7 @@ int qssm_scan_fwd(const void* x, const void* a, const void* b, const void* c, vo
 
     // Few chains, long sequence: single-pass chained kernel instead of aggregate + carry + scan.
     if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
-        const size_t need = chained_ws_bytes(B, L, D, in_dtype, false);
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype, out_dtype, false);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         if (need > 0 && ws_bytes >= need && tma_ok(x, B, L, D, in_stride_b, in_stride_l, es) &&
             tma_ok(a, B, L, D, in_stride_b, in_stride_l, es) && tma_ok(b, B, L, D, in_stride_b, in_stride_l, es) &&
@@ -930,7 +936,7 @@ int qssm_scan_fwd_static_ws(const void* x, const void* a, const void* b, const v
     const int n_seg = n_seg_req != 0 ? n_seg_req : auto_segments(B, L, D, in_dtype);
     size_t need = ws_bytes_for(B, D, n_seg);
     if (n_seg_req == 0 && h_saved == nullptr) {
-        const size_t chained = chained_ws_bytes(B, L, D, in_dtype, false);
+        const size_t chained = chained_ws_bytes(B, L, D, in_dtype, out_dtype, false);
         if (chained > need) need = chained;
     }
     if (need > (size_t)QSSM_STATIC_WS_BYTES) return QSSM_E_STATIC_WS;
@@ -967,7 +973,7 @@ int qssm_scan_bwd(const void* x, const void* a, const void* b, const void* c, co
 
     // Few chains, long sequence: single-pass chained kernel (h rebuilt from tile_h only).
     if (n_seg_req == 0 && h_saved == nullptr && ws != nullptr && knob(K_NO_TMA, 0) == 0) {
-        const size_t need = chained_ws_bytes(B, L, D, in_dtype, true);
+        const size_t need = chained_ws_bytes(B, L, D, in_dtype, out_dtype, true);
         const int es = dtype_size(in_dtype), eo = dtype_size(out_dtype);
         const long long n_tiles_b = (L + TS - 1) / TS;
         const long long g_sb = L * D, g_sl = D;

@@ -431,6 +431,19 @@ def test_fp32_launch_shapes_by_strip_count_match_float64(shape, route):
     _check(got, ref, torch.float32)
 
 
+@pytest.mark.parametrize("shape,dtype,out_dtype", [((5, 203, 4096), torch.bfloat16, None), ((6, 150, 4070), torch.float16, None),
+                                                   ((5, 203, 4096), torch.bfloat16, torch.float32)],
+                         ids=["bf16_320_strips", "fp16_384_strips_ragged", "bf16_320_strips_fp32_out"])
+def test_half_between_two_and_three_strips_per_sm_matches_fp32_loop(shape, dtype, out_dtype):
+    """16-bit storage with 2 to 2.75 strips per SM: the forward with 16-bit output runs one warp per strip on
+    32-row tiles while the backward (and the forward with fp32 output) stays on the chained kernels, so one
+    autograd step mixes the two routes through the same tile states."""
+    inp = make_inputs(*shape, dtype=dtype, out_dtype=out_dtype, seed=61)
+    ref = _oracle(inp, np.float32)
+    got = _run_scan(inp, out_dtype=out_dtype)
+    _check(got, ref, dtype)
+
+
 @pytest.mark.parametrize("shape,dtype,out_dtype", [((8, 200, 4096), torch.bfloat16, None),
                                                    ((8, 200, 4000), torch.float16, None),
                                                    ((9, 137, 3784), torch.bfloat16, torch.float32)],
