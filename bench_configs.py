@@ -97,7 +97,7 @@ def run_norm(args):
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    B, L, H = 16, 4096, 1024
+    B, L, H = 16, args.seq_len or 4096, 1024
     out = {"config": "cfg3_norm", "shape": [B, L, H]}
     for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
         g = torch.Generator(device=dev).manual_seed(0)
