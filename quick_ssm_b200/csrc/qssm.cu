@@ -1245,10 +1245,11 @@ int qssm_gated_scan_fwd(const void* pa, const void* px, const void* pc1, const v
         if (!tma_ok(t, B, L, D, in_stride_b, in_stride_l, es)) return QSSM_E_STRIDE;
     if (!tma_ok(y, B, L, D, out_stride_b, out_stride_l, eo)) return QSSM_E_STRIDE;
 
-    // 16-bit projection outputs: the kernels are bound by instruction issue, and twice as many warps on
-    // strips half as wide are faster (same shape as above: 1.79 ms against 2.11 ms); fp32 ones are not (3.34 / 2.85)
+    // 16-bit projection outputs with fp32 y: twice as many warps on strips half as wide are faster (16 x 4096 x 4096,
+    // forward 0.66 ms against 0.82 ms); with 16-bit y the wide strips win (0.50 against 0.69 ms), and with fp32
+    // projection outputs too (0.95 ms either way)
     Plan pl;
-    if ((rc = make_plan(pl, B, L, D, 1, status_word, dtype_size(in_dtype) == 2 ? 1 : 0))) return rc;
+    if ((rc = make_plan(pl, B, L, D, 1, status_word, es == 2 && eo == 4 ? 1 : 0))) return rc;
     pl.grid = concurrent_chains_gated(pl.chains);
     GatedFwdParams fp;
     memset(&fp, 0, sizeof(fp));
@@ -1297,8 +1298,8 @@ int qssm_gated_scan_bwd(const void* pa, const void* px, const void* pc1, const v
     if (!tma_ok(dy, B, L, D, dy_stride_b, dy_stride_l, eo) || !tma_ok(tile_h, B, n_tiles_b, D, n_tiles_b * D, D, 4))
         return QSSM_E_STRIDE;
 
-    // 16-bit projection outputs: the kernels are bound by instruction issue, and twice as many warps on
-    // strips half as wide are faster (same shape as above: 1.79 ms against 2.11 ms); fp32 ones are not (3.34 / 2.85)
+    // 16-bit projection outputs: twice as many warps on strips half as wide are faster (16 x 4096 x 4096, backward
+    // 1.15 ms against 1.31 ms with fp32 dy, 1.13 against 1.19 with 16-bit dy); fp32 ones are not (2.00 against 2.41)
     Plan pl;
     if ((rc = make_plan(pl, B, L, D, 1, status_word, dtype_size(in_dtype) == 2 ? 1 : 0))) return rc;
     pl.grid = concurrent_chains_gated(pl.chains);

@@ -169,10 +169,15 @@ def test_fused_gate_layer_matches_the_unfused_layer(param_dtype, compute_dtype):
 def test_gated_scan_matches_composition_of_torch_gates():
     from quick_ssm_b200.gated import _composed, gated_scan
     torch.manual_seed(1)
-    for dtype, gate, out in [(torch.float32, torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
-                             (torch.float16, torch.float16, torch.float32), (torch.float32, torch.float32, torch.float32)]:
-        pre = [torch.randn(2, 200, 136, device="cuda", dtype=dtype) for _ in range(5)]
-        dy = torch.randn(2, 200, 136, device="cuda", dtype=out)
+    # the last two shapes have enough strips for the wide-strip forward (16-bit y) next to the narrow-strip backward
+    for dtype, gate, out, shape in [(torch.float32, torch.bfloat16, torch.float32, (2, 200, 136)),
+                                    (torch.bfloat16, torch.bfloat16, torch.bfloat16, (2, 200, 136)),
+                                    (torch.float16, torch.float16, torch.float32, (2, 200, 136)),
+                                    (torch.float32, torch.float32, torch.float32, (2, 200, 136)),
+                                    (torch.bfloat16, torch.bfloat16, torch.bfloat16, (10, 70, 4096)),
+                                    (torch.float16, torch.float16, torch.float16, (9, 50, 4070))]:
+        pre = [torch.randn(*shape, device="cuda", dtype=dtype) for _ in range(5)]
+        dy = torch.randn(*shape, device="cuda", dtype=out)
         res = []
         for fn in (_composed, None):
             leaves = [t.clone().requires_grad_() for t in pre]
