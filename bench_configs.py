@@ -382,12 +382,7 @@ def main():
     res = dict(zip(keys, (float(v) for v in t.tolist())))
 
     if rank == 0:
-        try:
-            with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-                                   "MEASURED_PEAKS.json")) as f:
-                peak = float(json.load(f)["hbm_gbs"])
-        except Exception:
-            peak = 6650.0
+        peak = _copy_peak_gbs()
         extra = 0 if ckpt else 4
         bytes_fwd = 4 * s + so + extra
         bytes_bwd = 8 * s + so + extra
