@@ -137,8 +137,8 @@ def run_strips(args):
     dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]
     D = 2048
     peak = _copy_peak_gbs()
-    for B in (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 32):
-        L = ((1 << 27) // (B * D)) // 256 * 256
+    for B in ((args.batch,) if args.batch else (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 32)):
+        L = args.seq_len or ((1 << 27) // (B * D)) // 256 * 256
         inp = make_inputs(B, L, D, dtype=dtype, device=dev, seed=0)
         x, a, b, c = inp.tensors()
         y = torch.empty_like(x)
@@ -296,6 +296,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="cfg4", choices=sorted(CONFIGS) + ["cfg3_stack", "cfg3_gates", "cfg3_norm", "strips", "ref_triton"])
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16", "fp16"], help="strips: storage type")
+    ap.add_argument("--batch", type=int, default=0, help="strips: one batch size instead of the sweep (with --seq-len: a small case for a profiler)")
     ap.add_argument("--shard", default="none", choices=["none", "batch", "seq"])
     ap.add_argument("--no-checkpoint", action="store_true", help="store fp32 h in the forward instead of recomputing")
     ap.add_argument("--steps", type=int, default=10)
