@@ -110,11 +110,17 @@ def dtype_code(dt: torch.dtype) -> int:
 _status_words = {}   # device index -> (pinned tensor, its address, a ctypes view of the int)
 
 
+_status_lock = threading.Lock()
+
+
 def _status_entry(index: int):
     e = _status_words.get(index)
     if e is None:
-        w = torch.zeros(1, dtype=torch.int32).pin_memory()
-        e = _status_words[index] = (w, w.data_ptr(), ctypes.c_int.from_address(w.data_ptr()))
+        with _status_lock:  # two host threads may make their first call at the same time
+            e = _status_words.get(index)
+            if e is None:
+                w = torch.zeros(1, dtype=torch.int32).pin_memory()
+                e = _status_words[index] = (w, w.data_ptr(), ctypes.c_int.from_address(w.data_ptr()))
     return e
 
 

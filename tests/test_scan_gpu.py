@@ -510,3 +510,42 @@ def test_views_with_odd_offsets_and_pitches():
         for u, v in zip(*outs):
             assert torch.equal(u, v)
     _lib.check_device_status(synchronize=True)
+
+
+def test_two_host_threads_on_their_own_streams():
+    """Two host threads, each on its own CUDA stream, run forward + backward repeatedly on different shapes at
+    the same time (one few-strip shape on the chained kernels, one on the one-warp kernels): the per-thread
+    tensor-map cache, the shared kernel-attribute cache and the per-call workspaces must keep them apart."""
+    import threading
+    cases = [make_inputs(1, 6000, 192, dtype=torch.bfloat16, seed=71, decay="near_unit"),
+             make_inputs(6, 300, 2048, dtype=torch.float32, seed=73)]
+    refs = [_oracle(cases[0], np.float32), _oracle(cases[1], np.float64)]
+    results, errors = [None, None], []
+
+    def work(i):
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                dev = [t.to(DEV) for t in (*cases[i].tensors(), cases[i].dy)]
+                for _ in range(6):
+                    x, a, b, c = (t.detach().requires_grad_() for t in dev[:4])
+                    y = scan(x, a, b, c)
+                    y.backward(dev[4])
+                    results[i] = dict(y=y.detach(), dx=x.grad, da=a.grad, db=b.grad, dc=c.grad)
+                stream.synchronize()
+        except Exception as e:  # surfaced in the main thread below
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    _lib.check_device_status(synchronize=True)
+    for i, dt in enumerate((torch.bfloat16, torch.float32)):
+        if dt == torch.bfloat16:
+            for k in ("y", "dx", "da", "db", "dc"):
+                assert_close_half(results[i][k], refs[i][k], k, scale_atol=max(1.0, float(np.abs(refs[i][k]).max())))
+        else:
+            _check(results[i], refs[i], dt)
