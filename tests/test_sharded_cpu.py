@@ -75,7 +75,7 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 4])
 def test_sequence_shards_reproduce_the_whole_scan(tmp_path, world):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     parts = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
