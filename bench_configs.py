@@ -64,7 +64,7 @@ def run_gates(args):
 
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    B, L, D = 16, 4096, 4096
+    B, L, D = 16, args.seq_len or 4096, 4096
     out = {"config": "cfg3_gates", "shape": [B, L, D], "gate_dtype": "bfloat16", "scan_out_dtype": "float32"}
     for name, dtype in (("fp32_projections", torch.float32), ("bf16_projections", torch.bfloat16)):
         torch.manual_seed(0)
